@@ -1,0 +1,434 @@
+#!/usr/bin/env python
+"""TBE benchmark: forward + backward + fused optimizer, lookups/s and fraction of the HBM roofline.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload target] [--impl ours|reference]
+
+One "step" is one pass of the hot path over one batch of seeded synthetic lookups:
+pooled forward, then the backward with the optimizer fused into it.  The default workload is the
+headline target (T=64 tables of 1M rows, D=128 fp16, B=2048, L=38, uniform indices, exact SGD).
+With N > 1 (launched by torchrun, one rank per GPU) every rank owns 64 tables and looks up the
+global batch for them; pooled rows and gradients are exchanged through peer memory (weak scaling:
+the work per GPU is fixed, the number of tables grows with N).
+
+Rank 0 prints ONE JSON line.  ``value`` is device-resident throughput, ``e2e`` the same metric
+through the extension's function API with host buffers (H2D of indices/offsets/gradient and D2H of
+the pooled output inside the timed region), ``roofline`` describes the dominant kernel and
+``cpu_baseline`` is the reference's CPU path (per-table torch.nn.EmbeddingBag) timed on this host.
+``--impl reference`` times only that CPU path.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from sparse_ads_baselines_b200 import workloads  # noqa: E402
+
+METRIC = "TBE fwd+bwd+SGD lookups/s"
+UNIT = "lookups/s"
+ROTATE = 4  # distinct index batches cycled through the timed steps
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def __enter__(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if not self.path or not os.path.exists(self.path):
+            return out
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    smax.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(smax), samples=len(sm))
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+# ------------------------------------------------------------------ CPU reference path
+def cpu_reference_run(w, steps, warmup, budget_s=20.0):
+    """Times the reference's CPU path -- one torch.nn.EmbeddingBag(sparse=True) per table, forward,
+    backward, sparse SGD -- on a bounded sample of the workload: T_cpu tables of the same E, D, B, L
+    and index distribution.  Lookups/s does not depend on how many independent tables are looped
+    over, so the sample's rate stands for the workload's."""
+    from oracle import tbe_oracle as oracle
+    T_cpu = min(w.T, 4)
+    dtype = torch.float16 if w.dtype == "fp16" else torch.float32
+    note = ""
+    torch.set_num_threads(os.cpu_count() or 1)
+    indices, offsets = workloads.make_inputs(w, T=T_cpu)
+    offsets64 = offsets.astype(np.int64)
+    per_idx, per_off = [], []
+    for t in range(T_cpu):
+        lo, hi = int(offsets64[t * w.B]), int(offsets64[(t + 1) * w.B])
+        per_idx.append(torch.from_numpy(indices[lo:hi].astype(np.int64)))
+        per_off.append(torch.from_numpy(offsets64[t * w.B:(t + 1) * w.B] - lo))
+    backward = w.optimizer != "none"
+
+    def build(dt):
+        bags = oracle.PerTableEmbeddingBags(T_cpu, w.E, w.D, dtype=dt, pooling_mode=w.pooling, seed=0)
+        grads = [torch.randn(w.B, w.D).to(dt) for _ in range(T_cpu)]
+        return bags, grads
+
+    bags, grads = build(dtype)
+    try:
+        bags.step(per_idx, per_off, grads, w.lr, backward)
+    except RuntimeError as e:  # a dtype the CPU kernels lack
+        note = " (fp32 tables: %s)" % str(e).splitlines()[0][:60]
+        bags, grads = build(torch.float32)
+        bags.step(per_idx, per_off, grads, w.lr, backward)
+    for _ in range(max(warmup - 1, 0)):
+        bags.step(per_idx, per_off, grads, w.lr, backward)
+    times = []
+    t_begin = time.perf_counter()
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        bags.step(per_idx, per_off, grads, w.lr, backward)
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() - t_begin > budget_s:
+            break
+    n_lookups = int(offsets64[T_cpu * w.B])
+    total = sum(times)
+    return {
+        "value": n_lookups * len(times) / total,
+        "unit": UNIT,
+        "cores": torch.get_num_threads(),
+        "kind": "port",
+        "sample": "%d of %d tables (same E=%d, D=%d, B=%d, L, dtype, index distribution), %d timed steps of "
+                  "per-table torch.nn.EmbeddingBag fwd+bwd+sparse SGD%s" % (T_cpu, w.T, w.E, w.D, w.B, len(times), note),
+        "ms_per_step": 1e3 * total / len(times),
+        "steps": len(times),
+        "os_cpu_count": os.cpu_count(),
+    }
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    w = workloads.WORKLOADS[args.workload]
+    base = cpu_reference_run(w, args.steps, args.warmup, budget_s=120.0)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": base["steps"], "warmup": args.warmup, "ms_per_step": base["ms_per_step"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
+        "config": {"workload": describe(w, args.gpus)},
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def describe(w, n_gpus):
+    L = "L=%d" % w.L if w.L_dist == "fixed" else "L~Poisson(%g) in [%d,%d]" % (w.L_mean, w.L_min, w.L_max)
+    idx = "uniform" if w.index_dist == "uniform" else "Zipf(%g)" % w.zipf_alpha
+    return ("%s: T=%d tables/GPU x %d GPU, E=%d, D=%d %s, global B=%d, %s, %s indices, %s pooling, optimizer=%s"
+            % (w.name, w.T, n_gpus, w.E, w.D, w.dtype, w.B, L, idx, w.pooling, w.optimizer))
+
+
+# ------------------------------------------------------------------ GPU path
+def init_tables(module, w, seed):
+    """U(-0.01, 0.01) weights, filled table by table to avoid a full-size fp32 temporary."""
+    gen = torch.Generator(device=module.embedding_weights.device).manual_seed(seed)
+    data = module.embedding_weights.data
+    for t in range(w.T):
+        block = data[t * w.E:(t + 1) * w.E]
+        block.copy_(torch.rand(block.shape, device=data.device, generator=gen) * 0.02 - 0.01)
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+    from sparse_ads_baselines_b200 import _lib
+    from sparse_ads_baselines_b200 import table_batched_embeddings as tbe
+    from sparse_ads_baselines_b200 import table_batched_embeddings_ops as ops
+    from sparse_ads_baselines_b200.sharded import TableShardedEmbeddingBags
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path (use --impl reference for the CPU baseline)")
+    w = workloads.WORKLOADS[args.workload]
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    fp16 = w.dtype == "fp16"
+    tdt = torch.float16 if fp16 else torch.float32
+    opt = {"sgd": ops.Optimizer.SGD, "none": ops.Optimizer.SGD,
+           "exact_rowwise_adagrad": ops.Optimizer.EXACT_ROWWISE_ADAGRAD}[w.optimizer]
+    backward = w.optimizer != "none"
+    Bl = w.B // world
+    assert w.B % world == 0
+
+    sharded = TableShardedEmbeddingBags(w.T, w.E, w.D, w.B, optimizer=opt, learning_rate=w.lr, eps=w.eps, fp16=fp16,
+                                        pooling_mode=w.pooling, exchange=args.exchange).to(device)
+    module = sharded.tbe
+    init_tables(module, w, seed=1234 + rank)
+
+    # ROTATE distinct batches; every rank draws the global batch for its own tables
+    batches = []
+    for r in range(ROTATE):
+        idx, off = workloads.make_inputs(w, seed=w.seed + 1000 * rank + r)
+        idx_d, off_d = torch.from_numpy(idx).to(device), torch.from_numpy(off).to(device)
+        table_of_pos = torch.repeat_interleave(torch.arange(w.T * w.B, device=device) // w.B,
+                                               (off_d[1:] - off_d[:-1]).long())
+        U = int(torch.unique(table_of_pos * w.E + idx_d.long()).numel())
+        batches.append(dict(idx=idx_d, off=off_d, N=int(idx.size), U=U, idx_h=torch.from_numpy(idx).pin_memory(),
+                            off_h=torch.from_numpy(off).pin_memory()))
+        del table_of_pos
+    gen = torch.Generator(device=device).manual_seed(99 + rank)
+    grad = torch.randn(Bl, w.T * world, w.D, device=device, generator=gen).to(tdt)  # upstream gradient, local slice
+    N = batches[0]["N"]
+    nbags = w.T * w.B
+
+    def step(i):
+        b = batches[i % ROTATE]
+        if world == 1 and not backward:
+            with torch.no_grad():
+                module(b["idx"], b["off"])
+            return
+        out = sharded(b["idx"], b["off"])
+        if backward:
+            out.backward(grad)
+
+    def timed(n_steps):
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(n_steps):
+            step(i)
+        stop.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ms = torch.tensor([start.elapsed_time(stop)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for i in range(args.warmup):
+        step(i)
+    launches0 = _lib.lib().tbe_kernel_launch_count()
+    with ClockSampler(local_rank) as clocks:
+        total_ms = timed(args.steps)
+    launches = _lib.lib().tbe_kernel_launch_count() - launches0
+    ms_per_step = total_ms / args.steps
+    value = N * world / (ms_per_step * 1e-3)
+
+    # second, identical pass with per-launch events for the per-kernel breakdown
+    _lib.kernel_timing_enable(True)
+    timed(args.steps)
+    kt = _lib.kernel_timing_read()
+    _lib.kernel_timing_enable(False)
+
+    peak, peak_kind = measured_peaks()
+    U_mean = sum(b["U"] for b in batches) / ROTATE
+    alg = workloads.algorithmic_bytes(w, N, U_mean, nbags, backward)
+    kernel_bytes = {"tbe_forward_kernel": alg["fwd"], "segment_kernel": alg["bwd"]}
+    top = max((k for k in kt if k in kernel_bytes), key=lambda k: kt[k][1])
+    top_ms = kt[top][1] / kt[top][0]
+    achieved = kernel_bytes[top] / (top_ms * 1e-3) / 1e9
+    roofline = {
+        "bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+        "peak_kind": peak_kind, "traffic": args.traffic, "algorithmic_bytes_per_launch": kernel_bytes[top],
+        "avg_launch_ms": top_ms,
+        "step": {"algorithmic_bytes": alg["step"], "achieved": alg["step"] / (ms_per_step * 1e-3) / 1e9,
+                 "frac": alg["step"] / (ms_per_step * 1e-3) / 1e9 / peak,
+                 "frac_of_nominal_8TBs": alg["step"] / (ms_per_step * 1e-3) / 1e9 / 8000.0},
+        "kernels_ms_per_step": {k: v[1] / args.steps for k, v in sorted(kt.items())},
+    }
+
+    # end to end through the extension functions with host buffers (N = 1 only: the exchange needs
+    # device-resident peers)
+    e2e = None
+    if world == 1:
+        e2e = run_e2e(args, w, module, batches, grad, backward, tbe, device)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_reference_run(w, steps=8, warmup=1, budget_s=20.0)
+        cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
+            "config": {"workload": describe(w, world), "lookups_per_step": N * world, "unique_rows_per_step": U_mean,
+                       "exchange": args.exchange if world > 1 else "none",
+                       "l2": "inputs larger than L2: %.1f GB of tables per GPU, %d rotating index batches"
+                             % (w.T * w.E * w.D * w.elem_bytes / 1e9, ROTATE),
+                       "lookup_bytes_per_step_reference_convention": workloads.lookup_bytes(w, N, backward)},
+            "clocks": clocks.summary(), "roofline": roofline, "gpu_launches": int(launches),
+            "library_launches_note": "gpu_launches counts this library's own kernels; CUB sort/select launches are extra",
+        }
+        if e2e is not None:
+            line["e2e"] = e2e
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line))
+
+
+def run_e2e(args, w, module, batches, grad, backward, tbe, device):
+    """Host buffers in, host buffer out: per step the indices, offsets and upstream gradient are
+    copied from pinned host memory, the pooled output is copied back, all inside the timed region.
+    Copies run on their own streams and are double-buffered against the kernels."""
+    depth = 2
+    N = batches[0]["N"]
+    nbags = w.T * w.B
+    grad_h = grad.cpu().pin_memory()
+    weights, to = module.embedding_weights.data, module.table_offsets
+    d_idx = [torch.empty(N, dtype=torch.int32, device=device) for _ in range(depth)]
+    d_off = [torch.empty(nbags + 1, dtype=torch.int32, device=device) for _ in range(depth)]
+    d_grad = [torch.empty_like(grad) for _ in range(depth)]
+    d_out = [torch.empty(w.B, w.T, w.D, dtype=grad.dtype, device=device) for _ in range(depth)]
+    h_out = [torch.empty(w.B, w.T, w.D, dtype=grad.dtype).pin_memory() for _ in range(depth)]
+    s_in, s_out, s_main = torch.cuda.Stream(device), torch.cuda.Stream(device), torch.cuda.current_stream(device)
+    ev_in = [torch.cuda.Event() for _ in range(depth)]
+    ev_fwd = [torch.cuda.Event() for _ in range(depth)]
+    ev_done = [torch.cuda.Event() for _ in range(depth)]
+    ev_out = [torch.cuda.Event() for _ in range(depth)]
+    h2d = (N + nbags + 1) * 4 + (grad.numel() * grad.element_size() if backward else 0)
+    d2h = w.B * w.T * w.D * grad.element_size()
+
+    def run(n_steps):
+        for i in range(n_steps):
+            s = i % depth
+            b = batches[i % ROTATE]
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_done[s])  # slot's previous kernels are finished
+                d_idx[s].copy_(b["idx_h"], non_blocking=True)
+                d_off[s].copy_(b["off_h"], non_blocking=True)
+                if backward:
+                    d_grad[s].copy_(grad_h, non_blocking=True)
+                ev_in[s].record(s_in)
+            s_main.wait_event(ev_in[s])
+            s_main.wait_event(ev_out[s])  # slot's previous output has left the device
+            tbe.forward(weights, to, d_idx[s], d_off[s], None, 200, 2, False, pooling_mode=w.pooling, out=d_out[s])
+            ev_fwd[s].record(s_main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_fwd[s])
+                h_out[s].copy_(d_out[s], non_blocking=True)
+                ev_out[s].record(s_out)
+            if backward:
+                if w.optimizer == "sgd":
+                    tbe.backward_sgd(d_grad[s], weights, to, d_idx[s], d_off[s], w.lr, 200, 2, False,
+                                     pooling_mode=w.pooling)
+                else:
+                    tbe.backward_exact_adagrad(d_grad[s], weights, to, d_idx[s], d_off[s], None,
+                                               module.optimizer_state, w.lr, w.eps, False, 1, pooling_mode=w.pooling)
+            ev_done[s].record(s_main)
+
+    run(max(args.warmup, depth))
+    torch.cuda.synchronize()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record(s_main)
+    run(args.steps)
+    s_main.wait_stream(s_out)
+    s_main.wait_stream(s_in)
+    t1.record(s_main)
+    torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1) / args.steps
+    return {"value": N / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, "h2d_bytes_per_step": int(h2d),
+            "d2h_bytes_per_step": int(d2h),
+            "api": "table_batched_embeddings.forward/backward_* on pinned host buffers, double-buffered copies"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="target", choices=sorted(workloads.WORKLOADS))
+    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--traffic", type=float, default=None,
+                    help="DRAM bytes per launch of the dominant kernel from an ncu capture (profiles/), if known")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus:
+        if args.gpus == 1 and world == 1:
+            pass
+        else:
+            raise SystemExit("--gpus %d needs torchrun with %d ranks (WORLD_SIZE=%d)" % (args.gpus, args.gpus, world))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

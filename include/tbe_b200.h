@@ -1,0 +1,216 @@
+/*
+ * tbe_b200.h -- C ABI of libtbe_b200.so: table-batched embedding bags (TBE) for
+ * NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle
+ * (a cudaStream_t passed as void*; NULL = the legacy default stream).  Nothing
+ * here allocates device memory unless its comment says so: outputs, optimizer
+ * state and scratch ("workspace") are owned by the caller.  All work is enqueued
+ * on the given stream and the call returns without synchronising, unless noted.
+ *
+ * Return value: TBE_OK (0) or a negative tbe_status_t.  tbe_last_error_string()
+ * returns a thread-local description of the last failure on the calling thread.
+ *
+ * Data layout shared by all calls (it is the layout of the reference's
+ * table_batched_embeddings extension, table_batched_embeddings_cuda.cu:193-223):
+ *   weights        [total_rows][D] row-major, dtype = tbe_dtype_t
+ *   table_offsets  int32 [T]   first row of table t inside `weights`
+ *   indices        int32 [N]   row ids local to their table, bags flattened [T][B][L]
+ *   offsets        int32 [T*B+1] bag (t,b) owns indices[offsets[t*B+b] .. offsets[t*B+b+1])
+ *   output / grad  [B][T][D]   same dtype as weights
+ * Each citation "replaces <file>:<lines>" names the reference function whose
+ * pybind11 binding the entry point stands in for.
+ */
+#ifndef TBE_B200_H_
+#define TBE_B200_H_
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define TBE_API __attribute__((visibility("default")))
+#else
+#define TBE_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  TBE_OK = 0,
+  TBE_ERR_INVALID_ARGUMENT = -1, /* shape/dtype/alignment/null-pointer contract broken */
+  TBE_ERR_WORKSPACE_TOO_SMALL = -2,
+  TBE_ERR_CUDA = -3,             /* a CUDA runtime call or launch failed */
+  TBE_ERR_UNSUPPORTED = -4,      /* valid request this build does not implement */
+  TBE_ERR_BAD_INPUT_DATA = -5,   /* tbe_check_inputs found an index/offset violation */
+  TBE_ERR_TIMEOUT = -6           /* a bounded device-side wait ran out */
+} tbe_status_t;
+
+typedef enum { TBE_F32 = 0, TBE_F16 = 1, TBE_F64 = 2 } tbe_dtype_t;
+typedef enum { TBE_POOL_SUM = 0, TBE_POOL_MEAN = 1 } tbe_pooling_t;
+
+#define TBE_MAX_PEERS 16
+
+/* ---- library ---------------------------------------------------------- */
+
+/* Version of this ABI (bumped on any signature change). */
+TBE_API int tbe_abi_version(void);
+/* Thread-local text of the last error returned on this thread ("" if none). */
+TBE_API const char* tbe_last_error_string(void);
+/* Number of kernels of this library launched by this process so far (own kernels
+ * only; CUB sort/select launches are counted separately by tbe_library_launch_count). */
+TBE_API int64_t tbe_kernel_launch_count(void);
+TBE_API int64_t tbe_library_launch_count(void);
+/* Tuning knob for benchmarking sweeps: name in {"fwd_unroll","fwd_threads",
+ * "bwd_threads","bwd_unroll","long_segment"}; value 0 restores the default. */
+TBE_API int tbe_set_tuning(const char* name, int value);
+
+/* Per-launch timing for benchmarks: while enabled, every kernel launch of this library
+ * (and each CUB call) is bracketed by two CUDA events on its stream.  Enabling or
+ * disabling discards earlier records.  tbe_kernel_timing_read SYNCHRONISES on the
+ * recorded events, writes one "name launches total_ms" line per kernel into buffer
+ * (NUL-terminated), clears the records and returns the text length. */
+TBE_API int tbe_kernel_timing_enable(int on);
+TBE_API int64_t tbe_kernel_timing_read(char* buffer, int64_t buffer_bytes);
+
+/* ---- forward: pooled gather ------------------------------------------- */
+
+/* out[b][t][:] = sum_l w_l * weights[table_offsets[t] + indices[..l..]][:]  (mean: / L).
+ * per_sample_weights may be NULL (w_l = 1); with TBE_POOL_MEAN it must be NULL.
+ * Requires D % 4 == 0, T,B,D > 0.  Accumulates in fp32 (fp64 for TBE_F64) and
+ * rounds to nearest on store.
+ * replaces table_batched_embeddings_cuda.cu:253-316 (batched_embedding_forward_cuda). */
+TBE_API int tbe_forward(const void* weights, const int32_t* table_offsets,
+                const int32_t* indices, const int32_t* offsets,
+                const void* per_sample_weights, void* output,
+                int64_t T, int64_t B, int64_t D, int dtype, int pooling,
+                void* stream);
+
+/* Table-sharded forward with the all-to-all fused into the store: this rank owns
+ * T local tables (global columns t0 .. t0+T of T_total) and looks up the GLOBAL
+ * batch B for them; sample b belongs to rank b / (B / world) and its pooled row is
+ * written straight into that rank's buffer at
+ *   peer_outputs[b / B_local][(b % B_local)][t0 + t][:]     ([B_local][T_total][D])
+ * where peer_outputs[r] is a device pointer valid on THIS device (peer-mapped for
+ * r != own rank).  The caller orders this kernel against the consumers with its own
+ * barrier.  Layout contract of sparse_embedding_cuda.cpp:471-533
+ * (forward_all2all_nccl: out_j[b', r*T/W + t] = in_r[j*B/W + b', t]). */
+TBE_API int tbe_forward_sharded(const void* weights, const int32_t* table_offsets,
+                        const int32_t* indices, const int32_t* offsets,
+                        const void* per_sample_weights,
+                        void* const* peer_outputs, int world,
+                        int64_t T, int64_t B, int64_t D,
+                        int64_t T_total, int64_t t0,
+                        int dtype, int pooling, void* stream);
+
+/* All-to-all by direct peer stores: this rank holds src = [rows_local][world][chunk_bytes]
+ * and copies src[i][r] to peer_dst[r] + ((rank * rows_local + i) * chunk_bytes), i.e. every
+ * peer r ends up with dst_r = [world][rows_local][chunk_bytes].  peer_dst[r] are device
+ * pointers valid on this device (peer-mapped).  With rows_local = B/W and
+ * chunk_bytes = (T/W)*D*elem it is the gradient exchange of the table-sharded backward
+ * (All2AllFunction.backward, sparse_embedding_cuda_ops.py:104-117) without either of
+ * its transpose copies.  The caller orders it against the consumers with its own barrier.
+ * replaces sparse_embedding_cuda.cpp:471-533 (forward_all2all_nccl) on the backward path. */
+TBE_API int tbe_all2all_push(const void* src, void* const* peer_dst, int world, int rank,
+                             int64_t rows_local, int64_t chunk_bytes, void* stream);
+
+/* ---- backward with the optimizer fused into the write-back -------------- */
+
+/* Scratch bytes the backward calls need for N indices over total_rows rows. */
+TBE_API int64_t tbe_backward_workspace_bytes(int64_t N, int64_t total_rows);
+
+/* Exact (deterministic, duplicate-summing) SGD:
+ *   for every distinct row r touched: weights[r] -= lr * sum_{lookups of r} grad[b][t]
+ * (mean pooling: each term divided by its bag length).  grad_output element (b,t,d)
+ * is read at grad_output[b*stride_b + t*stride_t + d] (strides in elements), so the
+ * transposed view the all-to-all backward produces needs no copy.
+ * replaces table_batched_embeddings_cuda.cu:383-435 (batched_embedding_backward_sgd_cuda),
+ * whose per-lookup read-modify-write loses updates when a row repeats. */
+TBE_API int tbe_backward_sgd(const void* grad_output, int64_t stride_b, int64_t stride_t,
+                     void* weights, const int32_t* table_offsets,
+                     const int32_t* indices, const int32_t* offsets,
+                     int64_t T, int64_t B, int64_t D, int64_t N, int64_t total_rows,
+                     int dtype, int pooling, float lr,
+                     void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Exact rowwise Adagrad: per distinct row r with G = summed gradient,
+ *   state[r] += sum_d G_d^2;  weights[r] -= lr / (sqrt(state[r]) + eps) * G.
+ * stochastic_rounding applies to TBE_F16 only (13 random bits added below the fp16
+ * mantissa, then round-toward-zero), seeded by (sr_seed, sr_offset).
+ * replaces table_batched_embeddings_cuda.cu:1589-1705
+ * (batched_embedding_backward_adagrad_exact_cuda). */
+TBE_API int tbe_backward_exact_rowwise_adagrad(
+    const void* grad_output, int64_t stride_b, int64_t stride_t,
+    void* weights, const int32_t* table_offsets,
+    const int32_t* indices, const int32_t* offsets, float* optimizer_state,
+    int64_t T, int64_t B, int64_t D, int64_t N, int64_t total_rows,
+    int dtype, int pooling, float lr, float eps,
+    int stochastic_rounding, uint64_t sr_seed, uint64_t sr_offset,
+    void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Approximate rowwise Adagrad: every lookup is applied on its own, in index order,
+ * with its bag's g2 = |grad[b][t]|^2 (times w_l^2 when weighted):
+ *   state[r] += g2;  weights[r] -= w_l * lr / (sqrt(state[r]) + eps) * grad[b][t].
+ * grad_per_sample_weights (nullable unless per_sample_weights is given) receives
+ * <weights_before_update[r], grad[b][t]> per lookup.  Lookups of one row are applied
+ * in ascending index position, so the result is deterministic.
+ * replaces table_batched_embeddings_cuda.cu:706-793
+ * (batched_embedding_backward_adagrad_approx_cuda), whose updates race when a row repeats. */
+TBE_API int tbe_backward_approx_rowwise_adagrad(
+    const void* grad_output, int64_t stride_b, int64_t stride_t,
+    void* weights, const int32_t* table_offsets,
+    const int32_t* indices, const int32_t* offsets,
+    const void* per_sample_weights, void* grad_per_sample_weights,
+    float* optimizer_state,
+    int64_t T, int64_t B, int64_t D, int64_t N, int64_t total_rows,
+    int dtype, float lr, float eps,
+    int stochastic_rounding, uint64_t sr_seed, uint64_t sr_offset,
+    void* workspace, int64_t workspace_bytes, void* stream);
+
+/* The integer bookkeeping of the backward on its own (what the optimizer kernels
+ * consume): row ids sorted ascending, the bag id of each sorted entry, the start of
+ * each run of equal row ids and the number of runs.  Outputs are device arrays of
+ * N, N, N+1 and 1 int32; sorted_* and segment_starts may alias nothing in workspace.
+ * replaces table_batched_embeddings_cuda.cu:1471-1497,1638-1655
+ * (linear_index_weight_offsets_kernel + cub SortPairs) and the segment scan
+ * at :1523-1539. */
+TBE_API int tbe_sort_segments(const int32_t* table_offsets, const int32_t* indices,
+                      const int32_t* offsets,
+                      int64_t T, int64_t B, int64_t N, int64_t total_rows,
+                      int32_t* sorted_rows, int32_t* sorted_bags,
+                      int32_t* segment_starts, int32_t* num_segments,
+                      void* workspace, int64_t workspace_bytes, void* stream);
+
+/* ---- input helpers ------------------------------------------------------ */
+
+/* lengths_out[0] = 0; lengths_out[1 + t*B + b] = length of bag (t,b) given per-table
+ * begin offsets [T][B] and per-table totals [T]; the caller cumsums it.
+ * replaces table_batched_embeddings_cuda.cu:1190-1213 (construct_offsets). */
+TBE_API int tbe_construct_offsets(const int32_t* batch_offsets_per_table,
+                          const int32_t* total_indices_per_table,
+                          int32_t* lengths_out, int64_t T, int64_t B, void* stream);
+
+/* Validates indices/offsets on the device and SYNCHRONISES the stream: offsets[0]==0,
+ * non-decreasing, offsets[T*B]==N, 0 <= index < rows of its table (rows_per_table
+ * int32 [T]).  Returns TBE_ERR_BAD_INPUT_DATA with the first violation in the error
+ * string.  The reference has no such check (sparse_embedding_cuda_kernel.cu:212-214). */
+TBE_API int tbe_check_inputs(const int32_t* indices, const int32_t* offsets,
+                     const int32_t* rows_per_table,
+                     int64_t T, int64_t B, int64_t N, void* stream);
+
+/* ---- host-resident tables ------------------------------------------------ */
+
+/* Managed allocation preferred on the host and mapped for the current device
+ * (replaces CUDAManagedAllocator, table_batched_embeddings_cuda.cu:797-812), and a
+ * pinned, write-combined, device-mapped host allocation returning both addresses
+ * (replaces CUDAHostMappedAllocator, :820-838).  These DO allocate; free with the
+ * matching call. */
+TBE_API int tbe_alloc_managed(void** ptr, int64_t bytes);
+TBE_API int tbe_free_managed(void* ptr);
+TBE_API int tbe_alloc_host_mapped(void** host_ptr, void** device_ptr, int64_t bytes);
+TBE_API int tbe_free_host_mapped(void* host_ptr);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TBE_B200_H_ */

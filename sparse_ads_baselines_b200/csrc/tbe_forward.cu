@@ -1,0 +1,290 @@
+// Pooled embedding-bag forward (sum / mean, optional per-sample weights) for sm_100a.
+//
+// One warp owns one bag at a time and walks bags bag0, bag0+stride, ... (persistent
+// grid).  The warp keeps a three-deep software pipeline in registers: while the rows of
+// bag k are being gathered, the first 32 indices of bag k+1 and the offsets of bag k+2
+// are already in flight, so the offsets -> indices -> rows dependency chain is paid once
+// per warp instead of once per bag.  Indices are staged one per lane and broadcast with
+// shuffles; every lane issues UNROLL independent 16-byte streaming loads per step.
+// A row narrower than 32 vectors is owned by a sub-warp group, so a 256-byte row
+// (D=128 fp16) is fetched by half a warp and two rows are in flight per step.
+#include "tbe_common.cuh"
+
+namespace tbe {
+namespace {
+
+struct FwdArgs {
+  const void* weights;
+  const int32_t* table_offsets;
+  const int32_t* indices;
+  const int32_t* offsets;
+  const void* psw;
+  void* out[TBE_MAX_PEERS];  // out[0] only unless SHARDED
+  int32_t B, T, D;
+  int32_t B_local, T_total, t0;
+  int32_t lpr_log2, nvec, nchunks;
+};
+
+template <typename T>
+__device__ __forceinline__ typename Acc<T>::type to_acc(T x) {
+  return static_cast<typename Acc<T>::type>(x);
+}
+template <>
+__device__ __forceinline__ float to_acc<__half>(__half x) {
+  return __half2float(x);
+}
+
+template <typename T, int VB, bool WEIGHTED, bool MEAN, bool SHARDED, int UNROLL>
+__global__ void __launch_bounds__(256) tbe_forward_kernel(const FwdArgs a) {
+  using acc_t = typename Acc<T>::type;
+  constexpr int NE = VB / sizeof(T);
+
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int64_t nbags = static_cast<int64_t>(a.B) * a.T;
+  const int64_t wstride = static_cast<int64_t>(gridDim.x) * warps_per_block;
+  int64_t bag = static_cast<int64_t>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
+  if (bag >= nbags) return;
+
+  const int lpr_log2 = a.lpr_log2;
+  const int rps_log2 = 5 - lpr_log2;  // log2(rows per warp step)
+  const int sub = lane & ((1 << lpr_log2) - 1);
+  const int slot = lane >> lpr_log2;
+  const char* __restrict__ W = static_cast<const char*>(a.weights);
+  const int64_t row_bytes = static_cast<int64_t>(a.D) * sizeof(T);
+  const int32_t* __restrict__ offsets = a.offsets;
+  const int32_t* __restrict__ indices = a.indices;
+  const T* __restrict__ psw = static_cast<const T*>(a.psw);
+
+  // pipeline state: current bag fully described, next bag's extent known
+  int cur_s = __ldg(offsets + bag), cur_e = __ldg(offsets + bag + 1);
+  int cur_idx = (cur_s + lane < cur_e) ? __ldg(indices + cur_s + lane) : 0;
+  int64_t nbag = bag + wstride;
+  int nxt_s = 0, nxt_e = 0;
+  if (nbag < nbags) {
+    nxt_s = __ldg(offsets + nbag);
+    nxt_e = __ldg(offsets + nbag + 1);
+  }
+
+  while (true) {
+    // prefetch: indices of the next bag, extent of the one after it
+    const int64_t nnbag = nbag + wstride;
+    int pre_idx = 0, nn_s = 0, nn_e = 0;
+    if (nbag < nbags && nxt_s + lane < nxt_e) pre_idx = __ldg(indices + nxt_s + lane);
+    if (nnbag < nbags) {
+      nn_s = __ldg(offsets + nnbag);
+      nn_e = __ldg(offsets + nnbag + 1);
+    }
+
+    const int t = static_cast<int>(bag / a.B);
+    const int b = static_cast<int>(bag - static_cast<int64_t>(t) * a.B);
+    const int64_t row0 = __ldg(a.table_offsets + t);
+
+    char* outp;
+    if (SHARDED) {
+      const int dest = b / a.B_local;
+      const int bl = b - dest * a.B_local;
+      outp = static_cast<char*>(a.out[dest]) +
+             (static_cast<int64_t>(bl) * a.T_total + a.t0 + t) * row_bytes;
+    } else {
+      outp = static_cast<char*>(a.out[0]) + (static_cast<int64_t>(b) * a.T + t) * row_bytes;
+    }
+
+    for (int c = 0; c < a.nchunks; ++c) {
+      const int v = (c << 5) + sub;
+      const bool vact = v < a.nvec;
+      acc_t acc[NE];
+#pragma unroll
+      for (int k = 0; k < NE; ++k) acc[k] = 0;
+
+      for (int base = cur_s; base < cur_e; base += 32) {
+        int idx_l;
+        if (base == cur_s) {
+          idx_l = cur_idx;
+        } else {
+          idx_l = (base + lane < cur_e) ? __ldg(indices + base + lane) : 0;
+        }
+        acc_t w_l = 0;
+        if (WEIGHTED) {
+          if (base + lane < cur_e) w_l = to_acc<T>(psw[base + lane]);
+        }
+        const int cnt = min(32, cur_e - base);
+        const int steps = (cnt + (1 << rps_log2) - 1) >> rps_log2;
+        for (int s = 0; s < steps; s += UNROLL) {
+          Raw<VB> r[UNROLL];
+          acc_t w[UNROLL];
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) {
+            const int j = ((s + u) << rps_log2) + slot;
+            const int idx = __shfl_sync(kFullMask, idx_l, j & 31);
+            if (WEIGHTED) w[u] = __shfl_sync(kFullMask, w_l, j & 31);
+            if (j < cnt && vact) {
+              r[u] = ld_stream<VB>(W + (row0 + idx) * row_bytes + static_cast<int64_t>(v) * VB);
+            } else {
+              r[u] = raw_zero<VB>();
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) {
+            acc_t e[NE];
+            unpack<T, VB>(r[u], e);
+#pragma unroll
+            for (int k = 0; k < NE; ++k) {
+              if (WEIGHTED) {
+                acc[k] += e[k] * w[u];
+              } else {
+                acc[k] += e[k];
+              }
+            }
+          }
+        }
+      }
+      // fold the row slots of the warp together
+      for (int m = 1 << lpr_log2; m < 32; m <<= 1) {
+#pragma unroll
+        for (int k = 0; k < NE; ++k) acc[k] += __shfl_xor_sync(kFullMask, acc[k], m);
+      }
+      if (MEAN) {
+        const int L = cur_e - cur_s;
+        if (L > 0) {
+          const acc_t denom = static_cast<acc_t>(L);
+#pragma unroll
+          for (int k = 0; k < NE; ++k) acc[k] = acc[k] / denom;
+        }
+      }
+      if (slot == 0 && vact) st_row<VB>(outp + static_cast<int64_t>(v) * VB, pack_rn<T, VB>(acc));
+    }
+
+    bag = nbag;
+    if (bag >= nbags) break;
+    cur_s = nxt_s;
+    cur_e = nxt_e;
+    cur_idx = pre_idx;
+    nbag = nnbag;
+    nxt_s = nn_s;
+    nxt_e = nn_e;
+  }
+}
+
+template <typename T, int VB, bool WEIGHTED, bool MEAN, bool SHARDED, int UNROLL>
+int launch_fwd(const FwdArgs& a, cudaStream_t stream) {
+  auto kernel = tbe_forward_kernel<T, VB, WEIGHTED, MEAN, SHARDED, UNROLL>;
+  int threads = tuning(kTuneFwdThreads);
+  if (threads <= 0) threads = 256;
+  if (threads > 256 || threads % 32 != 0) return fail(TBE_ERR_INVALID_ARGUMENT, "fwd_threads must be a multiple of 32 <= 256");
+  int per_sm = 0;
+  TBE_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0));
+  if (per_sm < 1) per_sm = 1;
+  const int64_t nbags = static_cast<int64_t>(a.B) * a.T;
+  const int wpb = threads / 32;
+  int64_t blocks = (nbags + wpb - 1) / wpb;
+  const int64_t resident = static_cast<int64_t>(device_sm_count()) * per_sm;
+  if (blocks > resident) blocks = resident;
+  {
+    KernelTimer timer("tbe_forward_kernel", stream);
+    kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(a);
+  }
+  TBE_CHECK_LAUNCH("tbe_forward_kernel");
+  return TBE_OK;
+}
+
+template <typename T, int VB, bool SHARDED, int UNROLL>
+int dispatch_mode(const FwdArgs& a, bool weighted, bool mean, cudaStream_t stream) {
+  if (weighted) return launch_fwd<T, VB, true, false, SHARDED, UNROLL>(a, stream);
+  if (mean) return launch_fwd<T, VB, false, true, SHARDED, UNROLL>(a, stream);
+  return launch_fwd<T, VB, false, false, SHARDED, UNROLL>(a, stream);
+}
+
+template <bool SHARDED>
+int dispatch_fwd(const FwdArgs& a, int dtype, int vb, bool weighted, bool mean, cudaStream_t stream) {
+  const int unroll = tuning(kTuneFwdUnroll) > 0 ? tuning(kTuneFwdUnroll) : 4;
+  if (unroll != 4 && unroll != 8 && unroll != 2) return fail(TBE_ERR_INVALID_ARGUMENT, "fwd_unroll must be 2, 4 or 8");
+  switch (dtype) {
+    case TBE_F16:
+      if (vb == 16) {
+        if (unroll == 8) return dispatch_mode<__half, 16, SHARDED, 8>(a, weighted, mean, stream);
+        if (unroll == 2) return dispatch_mode<__half, 16, SHARDED, 2>(a, weighted, mean, stream);
+        return dispatch_mode<__half, 16, SHARDED, 4>(a, weighted, mean, stream);
+      }
+      return dispatch_mode<__half, 8, SHARDED, 4>(a, weighted, mean, stream);
+    case TBE_F32:
+      if (unroll == 8) return dispatch_mode<float, 16, SHARDED, 8>(a, weighted, mean, stream);
+      if (unroll == 2) return dispatch_mode<float, 16, SHARDED, 2>(a, weighted, mean, stream);
+      return dispatch_mode<float, 16, SHARDED, 4>(a, weighted, mean, stream);
+    case TBE_F64:
+      return dispatch_mode<double, 16, SHARDED, 4>(a, weighted, mean, stream);
+  }
+  return fail(TBE_ERR_INVALID_ARGUMENT, "unknown dtype %d", dtype);
+}
+
+int forward_common(const void* weights, const int32_t* table_offsets, const int32_t* indices,
+                   const int32_t* offsets, const void* psw, void* const* outs, int world,
+                   int64_t T, int64_t B, int64_t D, int64_t T_total, int64_t t0, int dtype,
+                   int pooling, bool sharded, void* stream) {
+  TBE_REQUIRE(weights && table_offsets && indices && offsets && outs, "tbe_forward: null pointer argument");
+  TBE_REQUIRE(T > 0, "tbe_forward: T must be > 0 (got %lld)", (long long)T);
+  TBE_REQUIRE(B > 0, "tbe_forward: B must be > 0 (got %lld)", (long long)B);
+  TBE_REQUIRE(D > 0 && D % 4 == 0, "tbe_forward: D must be a positive multiple of 4 (got %lld)", (long long)D);
+  TBE_REQUIRE(dtype == TBE_F32 || dtype == TBE_F16 || dtype == TBE_F64, "tbe_forward: bad dtype %d", dtype);
+  TBE_REQUIRE(pooling == TBE_POOL_SUM || pooling == TBE_POOL_MEAN, "tbe_forward: bad pooling %d", pooling);
+  TBE_REQUIRE(!(pooling == TBE_POOL_MEAN && psw), "tbe_forward: per-sample weights need sum pooling");
+  TBE_REQUIRE(B * T < (1ll << 31) && B * T_total * D / 1 > 0, "tbe_forward: B*T out of range");
+  TBE_REQUIRE(world >= 1 && world <= TBE_MAX_PEERS, "tbe_forward: world must be in [1,%d]", TBE_MAX_PEERS);
+  TBE_REQUIRE(B % world == 0, "tbe_forward: world (%d) must divide B (%lld)", world, (long long)B);
+  TBE_REQUIRE(t0 >= 0 && t0 + T <= T_total, "tbe_forward: table columns [%lld,%lld) outside T_total=%lld",
+              (long long)t0, (long long)(t0 + T), (long long)T_total);
+
+  FwdArgs a{};
+  a.weights = weights;
+  a.table_offsets = table_offsets;
+  a.indices = indices;
+  a.offsets = offsets;
+  a.psw = psw;
+  const void* align_probe = nullptr;
+  for (int r = 0; r < world; ++r) {
+    TBE_REQUIRE(outs[r] != nullptr, "tbe_forward: output pointer %d is null", r);
+    a.out[r] = outs[r];
+    if (reinterpret_cast<uintptr_t>(outs[r]) % 16 != 0) align_probe = outs[r];
+  }
+  a.B = static_cast<int32_t>(B);
+  a.T = static_cast<int32_t>(T);
+  a.D = static_cast<int32_t>(D);
+  a.B_local = static_cast<int32_t>(B / world);
+  a.T_total = static_cast<int32_t>(T_total);
+  a.t0 = static_cast<int32_t>(t0);
+  const RowGeom g = make_geom(D, dtype, weights, align_probe);
+  TBE_REQUIRE(g.vb == 16 || dtype == TBE_F16, "tbe_forward: weights/output must be 16-byte aligned");
+  if (g.vb == 8) {
+    TBE_REQUIRE(reinterpret_cast<uintptr_t>(weights) % 8 == 0, "tbe_forward: weights must be 8-byte aligned");
+    for (int r = 0; r < world; ++r)
+      TBE_REQUIRE(reinterpret_cast<uintptr_t>(outs[r]) % 8 == 0, "tbe_forward: output must be 8-byte aligned");
+  }
+  a.lpr_log2 = g.lpr_log2;
+  a.nvec = g.nvec;
+  a.nchunks = g.nchunks;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool weighted = psw != nullptr;
+  const bool mean = pooling == TBE_POOL_MEAN;
+  return sharded ? dispatch_fwd<true>(a, dtype, g.vb, weighted, mean, s)
+                 : dispatch_fwd<false>(a, dtype, g.vb, weighted, mean, s);
+}
+
+}  // namespace
+}  // namespace tbe
+
+extern "C" int tbe_forward(const void* weights, const int32_t* table_offsets, const int32_t* indices,
+                           const int32_t* offsets, const void* per_sample_weights, void* output,
+                           int64_t T, int64_t B, int64_t D, int dtype, int pooling, void* stream) {
+  void* outs[1] = {output};
+  return tbe::forward_common(weights, table_offsets, indices, offsets, per_sample_weights, outs, 1, T, B, D,
+                             T, 0, dtype, pooling, false, stream);
+}
+
+extern "C" int tbe_forward_sharded(const void* weights, const int32_t* table_offsets,
+                                   const int32_t* indices, const int32_t* offsets,
+                                   const void* per_sample_weights, void* const* peer_outputs, int world,
+                                   int64_t T, int64_t B, int64_t D, int64_t T_total, int64_t t0,
+                                   int dtype, int pooling, void* stream) {
+  return tbe::forward_common(weights, table_offsets, indices, offsets, per_sample_weights, peer_outputs,
+                             world, T, B, D, T_total, t0, dtype, pooling, true, stream);
+}

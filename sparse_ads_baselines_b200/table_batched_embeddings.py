@@ -1,0 +1,324 @@
+"""The functions of the reference's ``table_batched_embeddings`` extension module
+(table_batched_embeddings.cpp:56-70), bound to libtbe_b200.so.
+
+Same names, argument order and meaning as the reference's pybind11 module.  Tensors must live on a
+CUDA device; ``L_max``, ``BT_block_size`` and ``shmem`` are launch hints of the reference's kernels
+and are accepted and ignored (results never depend on them).  Everything is enqueued on the
+current CUDA stream of the weights' device and nothing synchronises.  Keyword-only extras
+(``pooling_mode``) default to the reference's behaviour.
+"""
+import ctypes
+import threading
+
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.float32: _lib.TBE_F32, torch.float16: _lib.TBE_F16, torch.float64: _lib.TBE_F64}
+_POOLING = {"sum": _lib.TBE_POOL_SUM, "mean": _lib.TBE_POOL_MEAN}
+
+_ws_lock = threading.Lock()
+_workspaces = {}  # (device index, stream handle) -> uint8 tensor
+
+
+def _require(cond, msg):
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _check_cuda(name, t, dtype=None):
+    _require(isinstance(t, torch.Tensor), "%s must be a tensor" % name)
+    _require(t.is_cuda, "%s must be a CUDA tensor (this library has no CPU path)" % name)
+    if dtype is not None:
+        _require(t.dtype == dtype, "%s must have dtype %s, got %s" % (name, dtype, t.dtype))
+
+
+def _stream(device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _workspace(device, nbytes):
+    """A cached scratch buffer per (device, stream); grows, never shrinks."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    with _ws_lock:
+        buf = _workspaces.get(key)
+        if buf is None or buf.numel() < nbytes:
+            buf = torch.empty(int(nbytes * 1.25) + 4096, dtype=torch.uint8, device=device)
+            _workspaces[key] = buf
+        return buf
+
+
+def release_workspaces():
+    """Drops every cached backward workspace."""
+    with _ws_lock:
+        _workspaces.clear()
+
+
+def _geometry(weights, table_offsets, offsets):
+    T = table_offsets.numel()
+    _require(T > 0, "table_offsets must not be empty")
+    _require(weights.dim() == 2, "weights must be [total_rows, D]")
+    D = weights.size(1)
+    _require(D > 0 and D % 4 == 0, "embedding dimension must be a positive multiple of 4, got %d" % D)
+    _require((offsets.numel() - 1) % T == 0, "offsets must have T*B+1 entries")
+    B = (offsets.numel() - 1) // T
+    _require(B > 0, "batch size must be > 0")
+    return T, B, D
+
+
+def _check_lookup_args(weights, table_offsets, indices, offsets):
+    _check_cuda("weights", weights)
+    _require(weights.dtype in _DTYPES, "weights must be float16, float32 or float64")
+    _require(weights.is_contiguous(), "weights must be contiguous")
+    _check_cuda("table_offsets", table_offsets, torch.int32)
+    _check_cuda("indices", indices, torch.int32)
+    _check_cuda("offsets", offsets, torch.int32)
+    for name, t in (("table_offsets", table_offsets), ("indices", indices), ("offsets", offsets)):
+        _require(t.device == weights.device, "%s is on %s but weights are on %s" % (name, t.device, weights.device))
+        _require(t.is_contiguous(), "%s must be contiguous" % name)
+
+
+def forward(weights, table_offsets, indices, offsets, indice_weights, L_max, BT_block_size, shmem, *,
+            pooling_mode="sum", out=None):
+    """Pooled lookup: returns ``[B, T, D]`` (reference: batched_embedding_forward_cuda,
+    table_batched_embeddings_cuda.cu:253-316)."""
+    _check_lookup_args(weights, table_offsets, indices, offsets)
+    T, B, D = _geometry(weights, table_offsets, offsets)
+    _require(BT_block_size != 0, "BT_block_size must not be 0")
+    _require(pooling_mode in _POOLING, "pooling_mode must be 'sum' or 'mean'")
+    psw = None
+    if indice_weights is not None:
+        _check_cuda("indice_weights", indice_weights, weights.dtype)
+        _require(indice_weights.numel() == indices.numel(), "indice_weights must have one entry per index")
+        psw = indice_weights.contiguous()
+    with torch.cuda.device(weights.device):
+        if out is None:
+            out = torch.empty((B, T, D), dtype=weights.dtype, device=weights.device)
+        else:
+            _require(out.shape == (B, T, D) and out.dtype == weights.dtype and out.is_contiguous()
+                     and out.device == weights.device, "out must be a contiguous [B, T, D] tensor like weights")
+        _lib.call("tbe_forward", weights.data_ptr(), table_offsets.data_ptr(), indices.data_ptr(),
+                  offsets.data_ptr(), psw.data_ptr() if psw is not None else None, out.data_ptr(),
+                  T, B, D, _DTYPES[weights.dtype], _POOLING[pooling_mode], _stream(weights.device))
+    return out
+
+
+def _grad_view(grad_output, B, T, D, weights):
+    _check_cuda("grad_output", grad_output, weights.dtype)
+    _require(tuple(grad_output.shape) == (B, T, D), "grad_output must be [B, T, D] = [%d, %d, %d], got %s"
+             % (B, T, D, tuple(grad_output.shape)))
+    _require(grad_output.device == weights.device, "grad_output must be on the weights' device")
+    if grad_output.stride(2) != 1 and D > 1:
+        grad_output = grad_output.contiguous()
+    return grad_output
+
+
+def _backward_workspace(weights, N, total_rows):
+    nbytes = _lib.lib().tbe_backward_workspace_bytes(N, total_rows)
+    if nbytes < 0:
+        raise _lib.TBEError("tbe_backward_workspace_bytes", nbytes, _lib.last_error())
+    return _workspace(weights.device, nbytes)
+
+
+def backward_sgd(grad_output, weights, table_offsets, indices, offsets, learning_rate, L_max, BT_block_size, shmem,
+                 *, pooling_mode="sum"):
+    """In-place exact SGD on ``weights`` (reference: batched_embedding_backward_sgd_cuda,
+    table_batched_embeddings_cuda.cu:383-435; here repeated rows are summed, not raced)."""
+    _check_lookup_args(weights, table_offsets, indices, offsets)
+    T, B, D = _geometry(weights, table_offsets, offsets)
+    _require(BT_block_size > 0, "BT_block_size must be > 0")
+    grad_output = _grad_view(grad_output, B, T, D, weights)
+    N = indices.numel()
+    with torch.cuda.device(weights.device):
+        ws = _backward_workspace(weights, N, weights.size(0))
+        _lib.call("tbe_backward_sgd", grad_output.data_ptr(), grad_output.stride(0), grad_output.stride(1),
+                  weights.data_ptr(), table_offsets.data_ptr(), indices.data_ptr(), offsets.data_ptr(),
+                  T, B, D, N, weights.size(0), _DTYPES[weights.dtype], _POOLING[pooling_mode],
+                  float(learning_rate), ws.data_ptr(), ws.numel(), _stream(weights.device))
+    return None
+
+
+def _philox_inputs(device, increment):
+    """(seed, offset) from the device's default generator, advancing it like a random op would."""
+    gen = torch.cuda.default_generators[device.index]
+    seed = gen.initial_seed()
+    offset = gen.get_offset()
+    gen.set_offset(offset + ((increment + 3) // 4) * 4)
+    return seed & 0xFFFFFFFFFFFFFFFF, offset
+
+
+def backward_exact_adagrad(grad_output, weights, table_offsets, indices, offsets, indice_weights, optimizer_state,
+                           learning_rate, eps, stochastic_rounding, BT_block_size, *, pooling_mode="sum"):
+    """In-place exact rowwise Adagrad (reference: batched_embedding_backward_adagrad_exact_cuda,
+    table_batched_embeddings_cuda.cu:1589-1705).  Like the reference, per-sample weights are not
+    supported by this optimizer."""
+    _check_lookup_args(weights, table_offsets, indices, offsets)
+    T, B, D = _geometry(weights, table_offsets, offsets)
+    _require(BT_block_size > 0, "BT_block_size must be > 0")
+    _require(indice_weights is None, "exact rowwise Adagrad does not support per-sample weights")
+    _check_cuda("optimizer_state", optimizer_state, torch.float32)
+    _require(optimizer_state.numel() == weights.size(0) and optimizer_state.is_contiguous(),
+             "optimizer_state must be a contiguous float32 [total_rows] tensor")
+    grad_output = _grad_view(grad_output, B, T, D, weights)
+    N = indices.numel()
+    seed, offset = (0, 0)
+    if stochastic_rounding and weights.dtype == torch.float16:
+        seed, offset = _philox_inputs(weights.device, 2 * ((D + 31) // 32))
+    with torch.cuda.device(weights.device):
+        ws = _backward_workspace(weights, N, weights.size(0))
+        _lib.call("tbe_backward_exact_rowwise_adagrad", grad_output.data_ptr(), grad_output.stride(0),
+                  grad_output.stride(1), weights.data_ptr(), table_offsets.data_ptr(), indices.data_ptr(),
+                  offsets.data_ptr(), optimizer_state.data_ptr(), T, B, D, N, weights.size(0),
+                  _DTYPES[weights.dtype], _POOLING[pooling_mode], float(learning_rate), float(eps),
+                  int(bool(stochastic_rounding)), seed, offset, ws.data_ptr(), ws.numel(),
+                  _stream(weights.device))
+    return None
+
+
+def backward_approx_adagrad(grad_output, weights, table_offsets, indices, offsets, indice_weights, optimizer_state,
+                            learning_rate, eps, L_max, stochastic_rounding, BT_block_size):
+    """In-place approximate rowwise Adagrad; returns the gradient of ``indice_weights`` or None
+    (reference: batched_embedding_backward_adagrad_approx_cuda,
+    table_batched_embeddings_cuda.cu:706-793)."""
+    _check_lookup_args(weights, table_offsets, indices, offsets)
+    T, B, D = _geometry(weights, table_offsets, offsets)
+    _require(BT_block_size > 0, "BT_block_size must be > 0")
+    _check_cuda("optimizer_state", optimizer_state, torch.float32)
+    _require(optimizer_state.numel() == weights.size(0) and optimizer_state.is_contiguous(),
+             "optimizer_state must be a contiguous float32 [total_rows] tensor")
+    grad_output = _grad_view(grad_output, B, T, D, weights)
+    N = indices.numel()
+    psw = grad_psw = None
+    if indice_weights is not None:
+        _check_cuda("indice_weights", indice_weights, weights.dtype)
+        _require(indice_weights.numel() == N, "indice_weights must have one entry per index")
+        psw = indice_weights.contiguous()
+        grad_psw = torch.empty(indices.shape, dtype=grad_output.dtype, device=weights.device)
+    seed, offset = (0, 0)
+    if stochastic_rounding and weights.dtype == torch.float16:
+        seed, offset = _philox_inputs(weights.device, 2 * ((D + 31) // 32))
+    with torch.cuda.device(weights.device):
+        ws = _backward_workspace(weights, N, weights.size(0))
+        _lib.call("tbe_backward_approx_rowwise_adagrad", grad_output.data_ptr(), grad_output.stride(0),
+                  grad_output.stride(1), weights.data_ptr(), table_offsets.data_ptr(), indices.data_ptr(),
+                  offsets.data_ptr(), psw.data_ptr() if psw is not None else None,
+                  grad_psw.data_ptr() if grad_psw is not None else None, optimizer_state.data_ptr(),
+                  T, B, D, N, weights.size(0), _DTYPES[weights.dtype], float(learning_rate), float(eps),
+                  int(bool(stochastic_rounding)), seed, offset, ws.data_ptr(), ws.numel(),
+                  _stream(weights.device))
+    return grad_psw
+
+
+def sort_segments(table_offsets, indices, offsets, total_rows):
+    """The backward's integer bookkeeping: ``(sorted_rows, sorted_bags, segment_starts)`` with
+    ``segment_starts`` trimmed to the number of distinct rows (synchronises to read that count)."""
+    _check_cuda("table_offsets", table_offsets, torch.int32)
+    _check_cuda("indices", indices, torch.int32)
+    _check_cuda("offsets", offsets, torch.int32)
+    T = table_offsets.numel()
+    B = (offsets.numel() - 1) // T
+    N = indices.numel()
+    dev = indices.device
+    with torch.cuda.device(dev):
+        rows = torch.empty(max(N, 1), dtype=torch.int32, device=dev)
+        bags = torch.empty(max(N, 1), dtype=torch.int32, device=dev)
+        starts = torch.empty(N + 1, dtype=torch.int32, device=dev)
+        count = torch.zeros(1, dtype=torch.int32, device=dev)
+        nbytes = _lib.lib().tbe_backward_workspace_bytes(N, total_rows)
+        if nbytes < 0:
+            raise _lib.TBEError("tbe_backward_workspace_bytes", nbytes, _lib.last_error())
+        ws = _workspace(dev, nbytes)
+        _lib.call("tbe_sort_segments", table_offsets.data_ptr(), indices.data_ptr(), offsets.data_ptr(),
+                  T, B, N, total_rows, rows.data_ptr(), bags.data_ptr(), starts.data_ptr(), count.data_ptr(),
+                  ws.data_ptr(), ws.numel(), _stream(dev))
+        u = int(count.item())
+    return rows[:N], bags[:N], starts[:u]
+
+
+def construct_offsets(batch_offsets_per_table, total_indices_per_table):
+    """``int32 [1 + T*B]`` with a leading 0 followed by every bag's length; the caller cumsums it
+    (reference: construct_offsets, table_batched_embeddings_cuda.cu:1190-1213)."""
+    _check_cuda("batch_offsets_per_table", batch_offsets_per_table, torch.int32)
+    _check_cuda("total_indices_per_table", total_indices_per_table, torch.int32)
+    _require(batch_offsets_per_table.dim() == 2, "batch_offsets_per_table must be [T, B]")
+    T, B = batch_offsets_per_table.shape
+    _require(total_indices_per_table.numel() == T, "total_indices_per_table must be [T]")
+    dev = batch_offsets_per_table.device
+    begin = batch_offsets_per_table.contiguous()
+    totals = total_indices_per_table.contiguous()
+    with torch.cuda.device(dev):
+        out = torch.empty(1 + T * B, dtype=torch.int32, device=dev)
+        _lib.call("tbe_construct_offsets", begin.data_ptr(), totals.data_ptr(), out.data_ptr(), T, B, _stream(dev))
+    return out
+
+
+def check_inputs(indices, offsets, rows_per_table):
+    """Raises if indices/offsets violate the layout contract (synchronises)."""
+    _check_cuda("indices", indices, torch.int32)
+    _check_cuda("offsets", offsets, torch.int32)
+    _check_cuda("rows_per_table", rows_per_table, torch.int32)
+    T = rows_per_table.numel()
+    _require((offsets.numel() - 1) % T == 0, "offsets must have T*B+1 entries")
+    B = (offsets.numel() - 1) // T
+    with torch.cuda.device(indices.device):
+        _lib.call("tbe_check_inputs", indices.data_ptr(), offsets.data_ptr(), rows_per_table.data_ptr(), T, B,
+                  indices.numel(), _stream(indices.device))
+
+
+class _RawCudaBuffer:
+    """Owns an allocation made by libtbe_b200 and exposes it through __cuda_array_interface__."""
+
+    def __init__(self, device_ptr, nbytes, free_fn, free_arg, typestr, shape):
+        self._free_fn, self._free_arg = free_fn, free_arg
+        self.device_ptr, self.nbytes = device_ptr, nbytes
+        self.__cuda_array_interface__ = {
+            "shape": tuple(shape), "typestr": typestr, "data": (device_ptr, False), "version": 2, "strides": None,
+        }
+
+    def __del__(self):
+        if self._free_fn is not None:
+            try:
+                getattr(_lib.lib(), self._free_fn)(ctypes.c_void_p(self._free_arg))
+            except Exception:
+                pass
+            self._free_fn = None
+
+
+_TYPESTR = {torch.float16: "<f2", torch.float32: "<f4", torch.float64: "<f8", torch.int32: "<i4", torch.int64: "<i8",
+            torch.uint8: "|u1"}
+
+
+def _numel(sizes):
+    n = 1
+    for s in sizes:
+        n *= int(s)
+    return n
+
+
+def new_managed_tensor(proto, sizes):
+    """A tensor of ``proto``'s dtype on ``proto``'s device backed by managed memory that prefers
+    host residency and is mapped into the device (reference: new_managed_tensor,
+    table_batched_embeddings_cuda.cu:864-871)."""
+    _check_cuda("proto", proto)
+    sizes = tuple(int(s) for s in sizes)
+    nbytes = max(_numel(sizes) * proto.element_size(), 1)
+    with torch.cuda.device(proto.device):
+        p = ctypes.c_void_p()
+        _lib.call("tbe_alloc_managed", ctypes.byref(p), nbytes)
+        holder = _RawCudaBuffer(p.value, nbytes, "tbe_free_managed", p.value, _TYPESTR[proto.dtype], sizes)
+        return torch.as_tensor(holder, device=proto.device)
+
+
+def new_host_mapped_tensor(proto, sizes):
+    """A tensor on ``proto``'s device whose storage is pinned host memory mapped into the device
+    (reference: new_host_mapped_tensor, table_batched_embeddings_cuda.cu:873-880)."""
+    _check_cuda("proto", proto)
+    sizes = tuple(int(s) for s in sizes)
+    nbytes = max(_numel(sizes) * proto.element_size(), 1)
+    with torch.cuda.device(proto.device):
+        h, d = ctypes.c_void_p(), ctypes.c_void_p()
+        _lib.call("tbe_alloc_host_mapped", ctypes.byref(h), ctypes.byref(d), nbytes)
+        holder = _RawCudaBuffer(d.value, nbytes, "tbe_free_host_mapped", h.value, _TYPESTR[proto.dtype], sizes)
+        t = torch.as_tensor(holder, device=proto.device)
+        t._tbe_host_ptr = h.value
+        return t

@@ -1,0 +1,122 @@
+"""Python op layer with the surface of the reference's ``table_batched_embeddings_ops``
+(table_batched_embeddings_ops.py:9-201): ``LookupFunction``, ``Optimizer``, ``EmbeddingLocation`` and
+``TableBatchedEmbeddingBags``; the optimizer step is fused into the backward, which updates
+``embedding_weights`` (and ``optimizer_state``) in place.
+
+Differences, all opt-in or fixes:
+  * ``pooling_mode="sum"|"mean"`` keyword (the reference only sums);
+  * SGD sums the gradients of repeated rows before the update (the reference's kernel races on
+    them, and its Python branch raises a TypeError at table_batched_embeddings_ops.py:66);
+  * tensors must be on a CUDA device: there is no CPU path.
+"""
+import enum
+import logging
+
+import numpy as np
+import torch
+from torch import nn
+
+from . import table_batched_embeddings
+
+
+class Optimizer(enum.Enum):
+    SGD = 1
+    APPROX_ROWWISE_ADAGRAD = 2
+    EXACT_ROWWISE_ADAGRAD = 3
+
+
+class EmbeddingLocation(enum.Enum):
+    DEVICE = 0
+    HOST_MAPPED = 1
+
+
+_L_MAX_HINT = 200  # launch hint of the reference's kernels; ignored by this library
+
+
+def _bt_block_hint(embedding_dim):
+    return max(256 // int(embedding_dim), 1)
+
+
+def _empty_sparse_grad(weights):
+    # The reference hands autograd an empty sparse tensor for the weights slot
+    # (table_batched_embeddings_ops.py:111): the real update already happened in place.
+    return torch.sparse_coo_tensor(size=tuple(weights.shape), dtype=weights.dtype, device=weights.device)
+
+
+class LookupFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, weights, table_offsets, indices, offsets, per_sample_weights, optimizer, optimizer_state,
+                learning_rate, eps, stochastic_rounding, pooling_mode="sum"):
+        ctx.optimizer = optimizer
+        ctx.learning_rate = learning_rate
+        ctx.eps = eps
+        ctx.stochastic_rounding = stochastic_rounding
+        ctx.pooling_mode = pooling_mode
+        ctx.save_for_backward(weights, table_offsets, indices, offsets, per_sample_weights, optimizer_state)
+        return table_batched_embeddings.forward(
+            weights, table_offsets, indices, offsets, per_sample_weights, _L_MAX_HINT,
+            _bt_block_hint(weights.shape[1]), False, pooling_mode=pooling_mode)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        weights, table_offsets, indices, offsets, per_sample_weights, optimizer_state = ctx.saved_tensors
+        assert ctx.optimizer in (Optimizer.SGD, Optimizer.APPROX_ROWWISE_ADAGRAD, Optimizer.EXACT_ROWWISE_ADAGRAD)
+        grad_per_sample_weight = None
+        if ctx.optimizer == Optimizer.SGD:
+            assert per_sample_weights is None
+            table_batched_embeddings.backward_sgd(
+                grad_output, weights, table_offsets, indices, offsets, ctx.learning_rate, _L_MAX_HINT,
+                _bt_block_hint(weights.shape[1]), False, pooling_mode=ctx.pooling_mode)
+        elif ctx.optimizer == Optimizer.APPROX_ROWWISE_ADAGRAD:
+            assert ctx.pooling_mode == "sum", "approximate rowwise Adagrad supports sum pooling only"
+            grad_per_sample_weight = table_batched_embeddings.backward_approx_adagrad(
+                grad_output, weights, table_offsets, indices, offsets, per_sample_weights, optimizer_state,
+                ctx.learning_rate, ctx.eps, _L_MAX_HINT, ctx.stochastic_rounding, 1)
+        else:
+            table_batched_embeddings.backward_exact_adagrad(
+                grad_output, weights, table_offsets, indices, offsets, per_sample_weights, optimizer_state,
+                ctx.learning_rate, ctx.eps, ctx.stochastic_rounding, 1, pooling_mode=ctx.pooling_mode)
+        return (_empty_sparse_grad(weights), None, None, None, grad_per_sample_weight, None, None, None, None,
+                None, None)
+
+
+class TableBatchedEmbeddingBags(nn.Module):
+    """T tables of ``num_embeddings`` rows and ``embedding_dim`` columns behind one lookup.
+
+    ``forward(indices, offsets[, per_sample_weights])`` takes int32 ``indices`` flattened as
+    ``[T][B][L]`` and int32 ``offsets`` of length ``T*B+1`` and returns ``[B, T, D]``.
+    """
+
+    def __init__(self, num_tables, num_embeddings, embedding_dim, optimizer=Optimizer.SGD, learning_rate=0.01,
+                 eps=None, stochastic_rounding=False, fp16=False, managed=EmbeddingLocation.DEVICE, *,
+                 pooling_mode="sum"):
+        super().__init__()
+        assert managed in (EmbeddingLocation.DEVICE, EmbeddingLocation.HOST_MAPPED)
+        assert pooling_mode in ("sum", "mean")
+        dtype = torch.float16 if fp16 else torch.float32
+        device = torch.device("cuda", torch.cuda.current_device())
+        total_rows = num_tables * num_embeddings
+        if managed == EmbeddingLocation.DEVICE:
+            logging.info("Allocating device embedding bag")
+            embedding_data = torch.randn(total_rows, embedding_dim, device=device, dtype=dtype)
+        else:
+            logging.info("Allocating host-mapped embedding bag")
+            proto = torch.empty(1, device=device, dtype=dtype)
+            embedding_data = table_batched_embeddings.new_managed_tensor(proto, (total_rows, embedding_dim))
+            embedding_data.normal_()
+        self.embedding_weights = nn.Parameter(embedding_data)
+        self.register_buffer(
+            "table_offsets",
+            torch.tensor([0] + np.cumsum([num_embeddings] * (num_tables - 1)).tolist(), dtype=torch.int32))
+        self.register_buffer("optimizer_state", torch.zeros(total_rows, dtype=torch.float32))
+        self.optimizer = optimizer
+        self.learning_rate = learning_rate
+        self.eps = eps
+        self.stochastic_rounding = stochastic_rounding
+        self.pooling_mode = pooling_mode
+
+    def forward(self, sharded_sparse_features, sharded_offsets, per_sample_weights=None):
+        return LookupFunction.apply(
+            self.embedding_weights, self.table_offsets, sharded_sparse_features, sharded_offsets,
+            per_sample_weights, self.optimizer, self.optimizer_state, self.learning_rate, self.eps,
+            self.stochastic_rounding, self.pooling_mode)
