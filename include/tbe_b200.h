@@ -119,11 +119,27 @@ TBE_API int tbe_all2all_push(const void* src, void* const* peer_dst, int world, 
 /* Scratch bytes the backward calls need for N indices over total_rows rows. */
 TBE_API int64_t tbe_backward_workspace_bytes(int64_t N, int64_t total_rows);
 
+/* The part of the backward that depends on the indices only: all N lookups sorted
+ * (stable) so that lookups of one row are adjacent, with the bag id of every sorted
+ * entry, left in `workspace`.  A backward call given the same workspace, the same
+ * max_rows_per_table and plan_ready = 1 skips this phase, so a caller can run it on
+ * another stream while the forward (or an exchange) is in flight.
+ * max_rows_per_table (0 = unknown) is the largest table's row count: when known, the
+ * sort only looks at ceil(log2(max_rows_per_table)) bits instead of
+ * ceil(log2(total_rows)), because lookups already arrive grouped by table.
+ * replaces table_batched_embeddings_cuda.cu:1471-1497,1638-1655
+ * (linear_index_weight_offsets_kernel + the two cub SortPairs calls). */
+TBE_API int tbe_backward_plan(const int32_t* table_offsets, const int32_t* indices,
+                              const int32_t* offsets, int64_t T, int64_t B, int64_t N,
+                              int64_t total_rows, int64_t max_rows_per_table,
+                              void* workspace, int64_t workspace_bytes, void* stream);
+
 /* Exact (deterministic, duplicate-summing) SGD:
  *   for every distinct row r touched: weights[r] -= lr * sum_{lookups of r} grad[b][t]
  * (mean pooling: each term divided by its bag length).  grad_output element (b,t,d)
  * is read at grad_output[b*stride_b + t*stride_t + d] (strides in elements), so the
- * transposed view the all-to-all backward produces needs no copy.
+ * transposed view the all-to-all backward produces needs no copy.  plan_ready != 0
+ * means `workspace` already holds tbe_backward_plan's result for these indices.
  * replaces table_batched_embeddings_cuda.cu:383-435 (batched_embedding_backward_sgd_cuda),
  * whose per-lookup read-modify-write loses updates when a row repeats. */
 TBE_API int tbe_backward_sgd(const void* grad_output, int64_t stride_b, int64_t stride_t,
@@ -131,6 +147,7 @@ TBE_API int tbe_backward_sgd(const void* grad_output, int64_t stride_b, int64_t 
                      const int32_t* indices, const int32_t* offsets,
                      int64_t T, int64_t B, int64_t D, int64_t N, int64_t total_rows,
                      int dtype, int pooling, float lr,
+                     int64_t max_rows_per_table, int plan_ready,
                      void* workspace, int64_t workspace_bytes, void* stream);
 
 /* Exact rowwise Adagrad: per distinct row r with G = summed gradient,
@@ -146,6 +163,7 @@ TBE_API int tbe_backward_exact_rowwise_adagrad(
     int64_t T, int64_t B, int64_t D, int64_t N, int64_t total_rows,
     int dtype, int pooling, float lr, float eps,
     int stochastic_rounding, uint64_t sr_seed, uint64_t sr_offset,
+    int64_t max_rows_per_table, int plan_ready,
     void* workspace, int64_t workspace_bytes, void* stream);
 
 /* Approximate rowwise Adagrad: every lookup is applied on its own, in index order,
@@ -170,7 +188,7 @@ TBE_API int tbe_backward_approx_rowwise_adagrad(
 /* The integer bookkeeping of the backward on its own (what the optimizer kernels
  * consume): row ids sorted ascending, the bag id of each sorted entry, the start of
  * each run of equal row ids and the number of runs.  Outputs are device arrays of
- * N, N, N+1 and 1 int32; sorted_* and segment_starts may alias nothing in workspace.
+ * N, N, N+1 and 1 int32 (the first *num_segments entries of segment_starts are set).
  * replaces table_batched_embeddings_cuda.cu:1471-1497,1638-1655
  * (linear_index_weight_offsets_kernel + cub SortPairs) and the segment scan
  * at :1523-1539. */

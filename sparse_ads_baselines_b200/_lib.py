@@ -30,10 +30,12 @@ SIGNATURES = {
                                    _i64, _i32, _i32, _vp]),
     "tbe_all2all_push": (_i32, [_vp, ctypes.POINTER(_vp), _i32, _i32, _i64, _i64, _vp]),
     "tbe_backward_workspace_bytes": (_i64, [_i64, _i64]),
+    "tbe_backward_plan": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     "tbe_backward_sgd": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _i32,
-                                _f32, _vp, _i64, _vp]),
+                                _f32, _i64, _i32, _vp, _i64, _vp]),
     "tbe_backward_exact_rowwise_adagrad": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64,
-                                                  _i64, _i32, _i32, _f32, _f32, _i32, _u64, _u64, _vp, _i64, _vp]),
+                                                  _i64, _i32, _i32, _f32, _f32, _i32, _u64, _u64, _i64, _i32, _vp,
+                                                  _i64, _vp]),
     "tbe_backward_approx_rowwise_adagrad": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                                                    _i64, _i64, _i64, _i32, _f32, _f32, _i32, _u64, _u64, _vp,
                                                    _i64, _vp]),

@@ -1,18 +1,27 @@
 // Deterministic TBE backward with the optimizer fused into the write-back (sm_100a).
 //
-// Pipeline per call (all on the caller's stream, scratch in the caller's workspace):
-//   1. linearize   : key[p] = table_offsets[t] + indices[p], value[p] = bag id (t*B+b)
-//   2. radix sort  : (key,value) pairs by key over ceil(log2(total_rows)) bits (CUB, stable,
-//                    so the entries of one row stay in ascending index position)
-//   3. run starts  : positions where the sorted key changes, compacted (CUB select)
-//   4. segment kernel: one lane group per run ("segment" = all lookups of one row):
-//                    G = sum of the bags' gradient rows in sorted order, then the optimizer
-//                    update of that row, written once.  Runs longer than `long_segment`
-//                    entries are queued and
-//   5. long-segment kernel: one CTA per queued run, lane groups sum strided slices, the
-//                    slices are folded in a fixed order in shared memory.
-// Every row is read once and written once; gradients of repeated rows are summed before
-// the update, so the result does not depend on scheduling.
+// Two phases, both on the caller's stream with scratch in the caller's workspace:
+//
+//  plan (depends on the indices only, so a caller may build it while the forward runs):
+//   1. linearize  : key[p] = table_offsets[t] + indices[p], value[p] = bag id (t*B+b)
+//   2. radix sort : (key,value) pairs by key over ceil(log2(total_rows)) bits (CUB, stable,
+//                   so the lookups of one row stay in ascending index position)
+//
+//  apply:
+//   3. run kernel : a warp walks 32 consecutive sorted entries at a time ("tile").  The tile's keys
+//                   and values are loaded coalesced, one per lane, and the next tile is prefetched
+//                   while this one is processed.  Run starts are found with one shuffle and a
+//                   ballot; every run that STARTS in the tile is owned by one lane group of the
+//                   warp, which already holds the row id and the bag ids in registers, so the
+//                   gradient rows and the weight row are requested without any dependent load.
+//                   G = sum of the run's gradient rows in sorted order; then the optimizer update
+//                   of the row, written once.  A run that continues past its tile is followed by
+//                   its owner; if it is longer than `long_segment` entries it is queued instead.
+//   4. long-run kernel: one CTA per queued run; lane groups sum strided slices that are folded in
+//                   a fixed order in shared memory.
+//
+// Every touched row is read once and written once; gradients of repeated rows are summed before
+// the update in an order fixed by the sort, so results do not depend on scheduling.
 #include <cub/device/device_radix_sort.cuh>
 #include <cub/device/device_select.cuh>
 #include <thrust/iterator/counting_iterator.h>
@@ -22,20 +31,20 @@
 namespace tbe {
 namespace {
 
-enum Opt { kSGD = 0, kExactAdagrad = 1, kApproxAdagrad = 2 };
+enum Opt { kSGD = 0, kExactAdagrad = 1 };
 
-constexpr int kDefaultLongSegment = 96;
+constexpr int kDefaultLongSegment = 64;
 constexpr int kBwdThreads = 256;
 
 // ------------------------------------------------------------------ workspace
 struct Workspace {
-  uint32_t* keys[2];
-  int32_t* vals[2];
-  int32_t* seg_starts;   // N + 1
-  int32_t* long_list;    // N / 2 + 1 (a run on the list has >= 2 entries)
-  int32_t* bag_of_pos;   // N (approx adagrad only)
-  float* bag_g2;         // unused slot kept for the approx path: sized by caller when needed
-  int32_t* counters;     // [0] = number of runs, [1] = number of long runs
+  uint32_t* keys_in;
+  uint32_t* keys;       // sorted row ids
+  int32_t* vals_in;
+  int32_t* vals;        // bag id of every sorted entry
+  int32_t* seg_starts;  // N + 1 (tbe_sort_segments only)
+  int2* long_list;      // {first sorted position, end position} of queued runs; N/32 + 2 entries
+  int32_t* counters;    // [0] = number of runs (tbe_sort_segments), [1] = queued long runs
   void* cub_temp;
   size_t cub_bytes;
   size_t total;
@@ -49,16 +58,16 @@ struct RunStart {
 
 size_t cub_temp_bytes(int64_t N, int end_bit, cudaError_t* err) {
   size_t sort_bytes = 0, sel_bytes = 0;
-  cub::DoubleBuffer<uint32_t> dk(nullptr, nullptr);
-  cub::DoubleBuffer<int32_t> dv(nullptr, nullptr);
-  cudaError_t e = cub::DeviceRadixSort::SortPairs(nullptr, sort_bytes, dk, dv, static_cast<int64_t>(N), 0, end_bit);
+  cudaError_t e = cub::DeviceRadixSort::SortPairs(nullptr, sort_bytes, static_cast<const uint32_t*>(nullptr),
+                                                  static_cast<uint32_t*>(nullptr), static_cast<const int32_t*>(nullptr),
+                                                  static_cast<int32_t*>(nullptr), static_cast<int64_t>(N), 0, end_bit);
   if (e != cudaSuccess) {
     *err = e;
     return 0;
   }
   thrust::counting_iterator<int32_t> it(0);
-  e = cub::DeviceSelect::If(nullptr, sel_bytes, it, static_cast<int32_t*>(nullptr),
-                            static_cast<int32_t*>(nullptr), static_cast<int64_t>(N), RunStart{nullptr});
+  e = cub::DeviceSelect::If(nullptr, sel_bytes, it, static_cast<int32_t*>(nullptr), static_cast<int32_t*>(nullptr),
+                            static_cast<int64_t>(N), RunStart{nullptr});
   if (e != cudaSuccess) {
     *err = e;
     return 0;
@@ -76,7 +85,7 @@ int key_bits(int64_t total_rows) {
 // Carves the workspace; with base == nullptr only sizes are computed.
 int carve(void* base, int64_t N, int64_t total_rows, Workspace* ws) {
   cudaError_t err = cudaSuccess;
-  const size_t cub_bytes = cub_temp_bytes(N > 0 ? N : 1, key_bits(total_rows), &err);
+  const size_t cub_bytes = cub_temp_bytes(N > 0 ? N : 1, 32, &err);
   if (err != cudaSuccess) return fail(TBE_ERR_CUDA, "CUB temp-storage query failed: %s", cudaGetErrorString(err));
   char* p = static_cast<char*>(base);
   size_t off = 0;
@@ -86,15 +95,13 @@ int carve(void* base, int64_t N, int64_t total_rows, Workspace* ws) {
     return r;
   };
   const size_t n = static_cast<size_t>(N > 0 ? N : 1);
-  ws->keys[0] = static_cast<uint32_t*>(take(n * 4));
-  ws->keys[1] = static_cast<uint32_t*>(take(n * 4));
-  ws->vals[0] = static_cast<int32_t*>(take(n * 4));
-  ws->vals[1] = static_cast<int32_t*>(take(n * 4));
-  ws->seg_starts = static_cast<int32_t*>(take((n + 1) * 4));
-  ws->long_list = static_cast<int32_t*>(take((n / 2 + 1) * 4));
-  ws->bag_of_pos = static_cast<int32_t*>(take(n * 4));
-  ws->bag_g2 = nullptr;
   ws->counters = static_cast<int32_t*>(take(64));
+  ws->keys = static_cast<uint32_t*>(take(n * 4));
+  ws->vals = static_cast<int32_t*>(take(n * 4));
+  ws->long_list = static_cast<int2*>(take((n / 32 + 2) * sizeof(int2)));
+  ws->keys_in = static_cast<uint32_t*>(take(n * 4));
+  ws->vals_in = static_cast<int32_t*>(take(n * 4));
+  ws->seg_starts = static_cast<int32_t*>(take((n + 1) * 4));
   ws->cub_temp = take(cub_bytes);
   ws->cub_bytes = cub_bytes;
   ws->total = off;
@@ -103,42 +110,55 @@ int carve(void* base, int64_t N, int64_t total_rows, Workspace* ws) {
 
 // ------------------------------------------------------------------ step 1: linearize
 // One warp per bag, lanes stride over the bag's index positions.
-template <bool WITH_POS>
 __global__ void __launch_bounds__(256) linearize_kernel(const int32_t* __restrict__ table_offsets,
                                                        const int32_t* __restrict__ indices,
                                                        const int32_t* __restrict__ offsets, int32_t B,
-                                                       int64_t nbags, uint32_t* __restrict__ keys,
-                                                       int32_t* __restrict__ vals,
-                                                       int32_t* __restrict__ bag_of_pos) {
+                                                       int64_t nbags, int idx_bits, uint32_t* __restrict__ keys,
+                                                       int32_t* __restrict__ vals) {
   const int lane = threadIdx.x & 31;
   const int64_t wstride = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
   for (int64_t bag = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); bag < nbags;
        bag += wstride) {
     const int t = static_cast<int>(bag / B);
-    const uint32_t row0 = static_cast<uint32_t>(__ldg(table_offsets + t));
+    // composite key (table << idx_bits | index) when idx_bits > 0, else the linear row id
+    const uint32_t row0 = idx_bits ? (static_cast<uint32_t>(t) << idx_bits) : static_cast<uint32_t>(__ldg(table_offsets + t));
     const int s = __ldg(offsets + bag), e = __ldg(offsets + bag + 1);
     for (int p = s + lane; p < e; p += 32) {
       keys[p] = row0 + static_cast<uint32_t>(__ldg(indices + p));
-      if (WITH_POS) {
-        vals[p] = p;
-        bag_of_pos[p] = static_cast<int32_t>(bag);
-      } else {
-        vals[p] = static_cast<int32_t>(bag);
-      }
+      vals[p] = static_cast<int32_t>(bag);
     }
   }
 }
 
-struct Plan {
-  const uint32_t* sorted_rows;
-  const int32_t* sorted_vals;
+// How the sort keys are formed.  Lookups arrive grouped by table, and a stable sort on the index
+// bits alone already brings equal (table, index) pairs together (ordered by index, then table), so
+// with composite keys only idx_bits need sorting instead of log2(total_rows).
+struct KeyLayout {
+  int idx_bits;   // 0: keys are linear row ids
+  int sort_bits;  // bits the radix sort looks at
 };
 
-// Steps 1-3.  Leaves ws.counters[0] = number of runs, ws.counters[1] = 0.
+KeyLayout key_layout(int64_t T, int64_t total_rows, int64_t max_rows_per_table, bool full_order) {
+  KeyLayout k;
+  int ib = 0, tb = 0;
+  if (max_rows_per_table > 0) {
+    ib = 1;
+    while (ib < 32 && (1ll << ib) < max_rows_per_table) ++ib;
+    while ((1ll << tb) < T) ++tb;
+  }
+  if (ib == 0 || ib + tb > 32) {
+    k.idx_bits = 0;
+    k.sort_bits = key_bits(total_rows);
+  } else {
+    k.idx_bits = ib;
+    k.sort_bits = full_order ? (ib + tb > 0 ? ib + tb : 1) : ib;
+  }
+  return k;
+}
+
+// Steps 1-2.  Leaves the sorted pairs in ws.keys / ws.vals.
 int build_plan(const int32_t* table_offsets, const int32_t* indices, const int32_t* offsets, int64_t T,
-               int64_t B, int64_t N, int64_t total_rows, bool with_pos, Workspace& ws, Plan* plan,
-               cudaStream_t stream) {
-  TBE_CUDA_TRY(cudaMemsetAsync(ws.counters, 0, 64, stream));
+               int64_t B, int64_t N, KeyLayout layout, Workspace& ws, cudaStream_t stream) {
   const int64_t nbags = T * B;
   {
     const int wpb = 256 / 32;
@@ -146,55 +166,39 @@ int build_plan(const int32_t* table_offsets, const int32_t* indices, const int32
     const int64_t cap = static_cast<int64_t>(device_sm_count()) * 16;
     if (blocks > cap) blocks = cap;
     KernelTimer timer("linearize_kernel", stream);
-    if (with_pos) {
-      linearize_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-          table_offsets, indices, offsets, static_cast<int32_t>(B), nbags, ws.keys[0], ws.vals[0], ws.bag_of_pos);
-    } else {
-      linearize_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-          table_offsets, indices, offsets, static_cast<int32_t>(B), nbags, ws.keys[0], ws.vals[0], nullptr);
-    }
+    linearize_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        table_offsets, indices, offsets, static_cast<int32_t>(B), nbags, layout.idx_bits, ws.keys_in, ws.vals_in);
   }
   TBE_CHECK_LAUNCH("linearize_kernel");
-  cub::DoubleBuffer<uint32_t> dk(ws.keys[0], ws.keys[1]);
-  cub::DoubleBuffer<int32_t> dv(ws.vals[0], ws.vals[1]);
   size_t bytes = ws.cub_bytes;
   {
     KernelTimer timer("cub_radix_sort_pairs", stream);
-    TBE_CUDA_TRY(cub::DeviceRadixSort::SortPairs(ws.cub_temp, bytes, dk, dv, static_cast<int64_t>(N), 0,
-                                                key_bits(total_rows), stream));
-  }
-  count_library_launch();
-  plan->sorted_rows = dk.Current();
-  plan->sorted_vals = dv.Current();
-  bytes = ws.cub_bytes;
-  thrust::counting_iterator<int32_t> it(0);
-  {
-    KernelTimer timer("cub_select_run_starts", stream);
-    TBE_CUDA_TRY(cub::DeviceSelect::If(ws.cub_temp, bytes, it, ws.seg_starts, ws.counters,
-                                       static_cast<int64_t>(N), RunStart{plan->sorted_rows}, stream));
+    TBE_CUDA_TRY(cub::DeviceRadixSort::SortPairs(ws.cub_temp, bytes, static_cast<const uint32_t*>(ws.keys_in),
+                                                ws.keys, static_cast<const int32_t*>(ws.vals_in), ws.vals,
+                                                static_cast<int64_t>(N), 0, layout.sort_bits, stream));
   }
   count_library_launch();
   return TBE_OK;
 }
 
-// ------------------------------------------------------------------ steps 4/5: segment kernels
+// ------------------------------------------------------------------ steps 3/4: run kernels
 struct BwdArgs {
   const void* grad;
   int64_t stride_b, stride_t;  // elements
   void* weights;
   float* state;
-  const uint32_t* sorted_rows;
-  const int32_t* sorted_vals;  // bag id (exact/SGD) or index position (approx)
-  const int32_t* seg_starts;
-  const int32_t* counters;     // [0] runs, [1] long runs
-  int32_t* long_list;
+  const uint32_t* keys;   // sorted row ids
+  const int32_t* vals;    // bag id of every sorted entry
+  int2* long_list;
   int32_t* long_count;
-  const int32_t* offsets;      // bag extents (mean pooling)
-  const int32_t* bag_of_pos;   // approx only
-  const void* psw;             // approx only, nullable
-  const float* bag_g2;         // approx only
+  const int32_t* offsets;  // bag extents (mean pooling)
+  const int32_t* table_offsets;
+  int32_t idx_bits;        // > 0: keys are (table << idx_bits | index)
+  FastDiv divB;            // bag id / B
   int32_t B, D, N;
-  int32_t lpr_log2, nvec, nchunks;
+  int32_t lpr_log2;          // run_kernel: lanes per row when a lane owns VPL vectors
+  int32_t lpr1_log2, nchunks;  // wide / long-run kernels: one vector per lane, rows walked in chunks
+  int32_t nvec;
   int32_t long_threshold;
   float lr, eps;
   uint64_t sr_seed, sr_offset;
@@ -229,49 +233,34 @@ __device__ __forceinline__ Raw<8> pack_out<__half, 8, true>(const float* v, Phil
   return r;
 }
 
-// Sums the gradient rows of entries [s + first, s + first + step, ...) < s + len of one run
-// for vector v of the row.  All lanes of the warp call this with a warp-uniform `iters`.
-template <typename T, int VB, bool MEAN, int UNROLL>
-__device__ __forceinline__ void sum_grads(const BwdArgs& a, int s, int len, int first, int step, int iters,
-                                          int v, bool vact, typename Acc<T>::type* acc) {
+// Requests vector v of the gradient row of `bag`; for mean pooling *scale receives 1/L of the bag.
+// Gradient rows are re-read once per lookup, so they are kept in L2 (evict-last policy `keep`).
+template <typename T, int VB, bool MEAN>
+__device__ __forceinline__ Raw<VB> load_grad(const BwdArgs& a, uint32_t bag, int v, uint64_t keep,
+                                             typename Acc<T>::type* scale) {
+  using acc_t = typename Acc<T>::type;
+  const uint32_t t = fastdiv(bag, a.divB);
+  const uint32_t b = bag - t * static_cast<uint32_t>(a.B);
+  if (MEAN) *scale = acc_t(1) / static_cast<acc_t>(__ldg(a.offsets + bag + 1) - __ldg(a.offsets + bag));
+  return ld_stream_hint<VB>(static_cast<const char*>(a.grad) +
+                                (static_cast<int64_t>(b) * a.stride_b + static_cast<int64_t>(t) * a.stride_t) *
+                                    static_cast<int64_t>(sizeof(T)) +
+                                static_cast<int64_t>(v) * VB,
+                            keep);
+}
+
+template <typename T, int VB, bool MEAN>
+__device__ __forceinline__ void add_grad(const Raw<VB>& r, typename Acc<T>::type scale, typename Acc<T>::type* acc) {
   using acc_t = typename Acc<T>::type;
   constexpr int NE = VB / sizeof(T);
-  const char* __restrict__ G = static_cast<const char*>(a.grad);
-  for (int it = 0; it < iters; it += UNROLL) {
-    Raw<VB> r[UNROLL];
-    acc_t sc[UNROLL];
+  acc_t e[NE];
+  unpack<T, VB>(r, e);
 #pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      const int i = first + (it + u) * step;
-      r[u] = raw_zero<VB>();
-      sc[u] = 1;
-      if (i < len) {
-        const uint32_t bag = static_cast<uint32_t>(__ldg(a.sorted_vals + s + i));
-        const uint32_t t = bag / static_cast<uint32_t>(a.B);
-        const uint32_t b = bag - t * static_cast<uint32_t>(a.B);
-        if (vact) {
-          r[u] = ld_stream<VB>(G + (static_cast<int64_t>(b) * a.stride_b + static_cast<int64_t>(t) * a.stride_t) *
-                                       static_cast<int64_t>(sizeof(T)) +
-                               static_cast<int64_t>(v) * VB);
-        }
-        if (MEAN) {
-          const int L = __ldg(a.offsets + bag + 1) - __ldg(a.offsets + bag);
-          sc[u] = static_cast<acc_t>(L);
-        }
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      acc_t e[NE];
-      unpack<T, VB>(r[u], e);
-#pragma unroll
-      for (int k = 0; k < NE; ++k) {
-        if (MEAN) {
-          acc[k] += e[k] / sc[u];
-        } else {
-          acc[k] += e[k];
-        }
-      }
+  for (int k = 0; k < NE; ++k) {
+    if (MEAN) {
+      acc[k] += e[k] * scale;
+    } else {
+      acc[k] += e[k];
     }
   }
 }
@@ -286,122 +275,469 @@ __device__ __forceinline__ A sq_sum(const A* v, int n) {
 // w -= mult * G for one vector, then store.
 template <typename T, int VB, bool SR>
 __device__ __forceinline__ void apply_update(char* wp, const Raw<VB>& wraw, const typename Acc<T>::type* G,
-                                             typename Acc<T>::type mult, Philox* rng) {
+                                             typename Acc<T>::type mult, Philox* rng, uint64_t streaming) {
   using acc_t = typename Acc<T>::type;
   constexpr int NE = VB / sizeof(T);
   acc_t w[NE];
   unpack<T, VB>(wraw, w);
 #pragma unroll
   for (int k = 0; k < NE; ++k) w[k] -= G[k] * mult;
-  st_row<VB>(wp, pack_out<T, VB, SR>(w, rng));
+  st_row_hint<VB>(wp, pack_out<T, VB, SR>(w, rng), streaming);
 }
 
-// One lane group per run.  OPT is kSGD or kExactAdagrad.
-template <typename T, int VB, int OPT, bool MEAN, bool SR, int UNROLL>
-__global__ void __launch_bounds__(kBwdThreads) segment_kernel(const BwdArgs a) {
+// Row of `weights` a sort key stands for.
+__device__ __forceinline__ uint32_t key_to_row(const BwdArgs& a, uint32_t key) {
+  if (a.idx_bits == 0) return key;
+  return static_cast<uint32_t>(__ldg(a.table_offsets + (key >> a.idx_bits))) + (key & ((1u << a.idx_bits) - 1u));
+}
+
+// First position >= lo in the sorted keys whose key differs from `row` (keys[lo-1] == row).
+__device__ __forceinline__ int run_end(const uint32_t* __restrict__ keys, int lo, int N, uint32_t row) {
+  int hi = N;
+  while (lo < hi) {
+    const int mid = lo + ((hi - lo) >> 1);
+    if (__ldg(keys + mid) == row) {
+      lo = mid + 1;
+    } else {
+      hi = mid;
+    }
+  }
+  return lo;
+}
+
+// Registers of one tile of 32 sorted entries: key/val of entry p0+lane and a halo word (lane 0: the
+// key before the tile, lane 31: the key after it).
+struct Tile {
+  uint32_t key, halo;
+  int32_t val;
+};
+
+__device__ __forceinline__ Tile load_tile(const uint32_t* __restrict__ keys, const int32_t* __restrict__ vals,
+                                          int64_t tile, int lane, int N) {
+  Tile t;
+  const int64_t p = (tile << 5) + lane;
+  t.key = 0xffffffffu;
+  t.val = 0;
+  t.halo = 0xffffffffu;
+  if (p < N) {
+    t.key = __ldg(keys + p);
+    t.val = __ldg(vals + p);
+  }
+  if (lane == 0 && p > 0) t.halo = __ldg(keys + p - 1);
+  if (lane == 31 && p + 1 < N) t.halo = __ldg(keys + p + 1);
+  return t;
+}
+
+// Rows of up to 32*VPL vectors (the common case).
+//
+// Work that is per sorted ENTRY is done by all 32 lanes at once, one entry per lane, once per tile:
+// decoding the key into a weight row, turning the bag id into the offset of its gradient row (and
+// 1/L for mean pooling), and measuring the run that starts at the lane.  Work that is per RUN is
+// done by a lane group that reads those per-lane results with shuffles: a run costs a handful of
+// shuffles, two address computations and its row loads.  A lane owns VPL vectors of a row (vector
+// sub, sub + lpr, ...: every load instruction of the warp covers contiguous 16*lpr-byte pieces), so
+// a 256-byte row needs only 4 lanes and a warp works on 8 runs at a time; each group keeps SEGS
+// runs in flight: the weight row, the optimizer state and the first two gradient rows of each are
+// requested first, then the runs are finished one after the other.
+template <typename T, int VB, int OPT, bool MEAN, bool SR, int SEGS, int VPL>
+__global__ void __launch_bounds__(kBwdThreads) run_kernel(const BwdArgs a) {
   using acc_t = typename Acc<T>::type;
   constexpr int NE = VB / sizeof(T);
   const int lane = threadIdx.x & 31;
   const int lpr_log2 = a.lpr_log2;
-  const int gpw = 32 >> lpr_log2;  // groups per warp
-  const int sub = lane & ((1 << lpr_log2) - 1);
+  const int lpr = 1 << lpr_log2;
+  const int sub = lane & (lpr - 1);
   const int slot = lane >> lpr_log2;
-  const int U = __ldg(a.counters);
-  const int64_t row_bytes = static_cast<int64_t>(a.D) * sizeof(T);
-  const int64_t warp_global = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int64_t warps_total = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  const int N = a.N;
+  const int64_t ntiles = (static_cast<int64_t>(N) + 31) >> 5;
+  const int64_t wstride = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  int64_t tile = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (tile >= ntiles) return;
+  const uint32_t row_bytes = static_cast<uint32_t>(a.D) * static_cast<uint32_t>(sizeof(T));
+  const uint32_t* __restrict__ keys = a.keys;
+  const int32_t* __restrict__ vals = a.vals;
+  // byte offset of this lane's j-th vector inside a row; lanes beyond the row's end re-read vector 0
+  // (a valid address) and never store
+  bool vact[VPL];
+  uint32_t voff[VPL];
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    const int v = sub + j * lpr;
+    vact[j] = v < a.nvec;
+    voff[j] = vact[j] ? static_cast<uint32_t>(v) * VB : 0u;
+  }
+  char* const wbase = static_cast<char*>(a.weights);
+  const char* const gbase = static_cast<const char*>(a.grad);
+  // gradient row offsets are kept in units of VB bytes so that they fit one 32-bit shuffle
+  const uint32_t sb_units = static_cast<uint32_t>(a.stride_b * static_cast<int64_t>(sizeof(T)) / VB);
+  const uint32_t st_units = static_cast<uint32_t>(a.stride_t * static_cast<int64_t>(sizeof(T)) / VB);
   Philox rng(a.sr_seed, static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x, a.sr_offset);
+  const uint64_t keep = l2_policy_evict_last(), streaming = l2_policy_evict_first();
+  // a lane group owns the runs that start in its own lanes of the tile
+  const unsigned own_lanes = (lpr_log2 == 5) ? kFullMask : (((1u << lpr) - 1u) << (slot << lpr_log2));
 
-  for (int64_t seg0 = warp_global * gpw; seg0 < U; seg0 += warps_total * gpw) {
-    const int64_t seg = seg0 + slot;
-    bool has = seg < U;
-    int s = 0, len = 0;
-    uint32_t row = 0;
-    if (has) {
-      s = __ldg(a.seg_starts + seg);
-      const int e = (seg + 1 < U) ? __ldg(a.seg_starts + seg + 1) : a.N;
-      len = e - s;
-      row = __ldg(a.sorted_rows + s);
-      if (len > a.long_threshold) {
-        if (sub == 0) a.long_list[atomicAdd(a.long_count, 1)] = static_cast<int32_t>(seg);
-        has = false;
-        len = 0;
+  // offset (in VB-byte units) of the gradient row of a bag, and 1/L of the bag for mean pooling
+  auto grad_units = [&](uint32_t bag, acc_t* scale) -> uint32_t {
+    const uint32_t t = fastdiv(bag, a.divB);
+    const uint32_t b = bag - t * static_cast<uint32_t>(a.B);
+    if (MEAN) *scale = acc_t(1) / static_cast<acc_t>(__ldg(a.offsets + bag + 1) - __ldg(a.offsets + bag));
+    return b * sb_units + t * st_units;
+  };
+  auto grad_ptr = [&](uint32_t units, int j) -> const char* {
+    return gbase + static_cast<uint64_t>(units) * static_cast<uint32_t>(VB) + voff[j];
+  };
+
+  Tile cur = load_tile(keys, vals, tile, lane, N);
+  while (true) {
+    const int64_t ntile = tile + wstride;
+    Tile nxt = cur;
+    if (ntile < ntiles) nxt = load_tile(keys, vals, ntile, lane, N);
+
+    // ---- per entry, all lanes at once
+    const int p0 = static_cast<int>(tile << 5);
+    const int nvalid = min(32, N - p0);
+    const bool valid = lane < nvalid;
+    uint32_t prev = __shfl_up_sync(kFullMask, cur.key, 1);
+    if (lane == 0) prev = cur.halo;
+    const bool is_start = valid && (p0 + lane == 0 || cur.key != prev);
+    const unsigned smask = __ballot_sync(kFullMask, is_start);
+    const unsigned above = (lane >= 31) ? 0u : (smask & ~((2u << lane) - 1u));
+    const int my_end = above ? (__ffs(above) - 1) : nvalid;  // first lane behind the run starting here
+    const int my_len = my_end - lane;
+    const uint32_t after = __shfl_sync(kFullMask, cur.halo, 31);
+    const bool crosses = is_start && my_end == 32 && p0 + 32 < N && after == cur.key;
+    const unsigned cmask = __ballot_sync(kFullMask, crosses);  // at most one bit
+    // invalid lanes describe entry 0 of the tile so that anything read through them is valid memory
+    const uint32_t key0 = __shfl_sync(kFullMask, cur.key, 0);
+    const int32_t val0 = __shfl_sync(kFullMask, cur.val, 0);
+    const uint32_t my_row = key_to_row(a, valid ? cur.key : key0);
+    acc_t my_scale = 1;
+    const uint32_t my_goff = grad_units(static_cast<uint32_t>(valid ? cur.val : val0), &my_scale);
+    unsigned mine = smask & own_lanes;
+    const int rounds = __reduce_max_sync(kFullMask, __popc(mine));
+
+    // ---- per run
+    for (int k = 0; k < rounds; k += SEGS) {
+      bool has[SEGS];
+      int first[SEGS], len[SEGS], tail_lo[SEGS], tail_hi[SEGS];
+      uint32_t wid[SEGS];
+      Raw<VB> wraw[SEGS][VPL], g0[SEGS][VPL], g1[SEGS][VPL];
+      acc_t s0[SEGS], s1[SEGS];
+      float st_old[SEGS];
+
+      // phase 1: pick the runs and request their rows (an idle group re-reads lane 0's rows)
+#pragma unroll
+      for (int q = 0; q < SEGS; ++q) {
+        has[q] = mine != 0u;
+        const int i = has[q] ? (__ffs(mine) - 1) : 0;
+        mine &= mine - 1u;  // (0 stays 0)
+        first[q] = i;
+        wid[q] = __shfl_sync(kFullMask, my_row, i);
+        len[q] = __shfl_sync(kFullMask, my_len, i);
+        if (!has[q]) len[q] = 0;
+        const uint32_t off0 = __shfl_sync(kFullMask, my_goff, i);
+        const uint32_t off1 = __shfl_sync(kFullMask, my_goff, (i + 1) & 31);
+        s0[q] = s1[q] = 1;
+        if (MEAN) {
+          s0[q] = __shfl_sync(kFullMask, my_scale, i);
+          s1[q] = __shfl_sync(kFullMask, my_scale, (i + 1) & 31);
+        }
+        tail_lo[q] = tail_hi[q] = 0;
+        if (has[q] && ((cmask >> i) & 1u)) {  // the run continues behind the tile (rare)
+          tail_lo[q] = p0 + 32;
+          tail_hi[q] = run_end(keys, tail_lo[q] + 1, N, after);
+          if (len[q] + (tail_hi[q] - tail_lo[q]) > a.long_threshold) {
+            if (sub == 0) a.long_list[atomicAdd(a.long_count, 1)] = make_int2(p0 + i, tail_hi[q]);
+            has[q] = false;
+            len[q] = 0;
+            tail_hi[q] = tail_lo[q];
+          }
+        }
+        const char* wrow = wbase + static_cast<uint64_t>(wid[q]) * row_bytes;
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+          wraw[q][j] = ld_rw_hint<VB>(wrow + voff[j], streaming);
+          g0[q][j] = ld_stream_hint<VB>(grad_ptr(off0, j), keep);
+          g1[q][j] = raw_zero<VB>();
+          if (len[q] > 1) g1[q][j] = ld_stream_hint<VB>(grad_ptr(off1, j), keep);
+        }
+        if (OPT == kExactAdagrad) st_old[q] = a.state[wid[q]];
+      }
+
+      // phase 2: finish the runs one by one
+#pragma unroll
+      for (int q = 0; q < SEGS; ++q) {
+        acc_t acc[VPL][NE];
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+          unpack<T, VB>(g0[q][j], acc[j]);
+          if (MEAN) {
+#pragma unroll
+            for (int kk = 0; kk < NE; ++kk) acc[j][kk] *= s0[q];
+          }
+        }
+        const int maxlen = __reduce_max_sync(kFullMask, len[q]);
+        if (maxlen > 1) {
+#pragma unroll
+          for (int j = 0; j < VPL; ++j) add_grad<T, VB, MEAN>(g1[q][j], s1[q], acc[j]);
+          for (int e = 2; e < maxlen; e += 2) {  // warp-uniform; runs of 3+ entries inside the tile
+            const uint32_t o0 = __shfl_sync(kFullMask, my_goff, (first[q] + e) & 31);
+            const uint32_t o1 = __shfl_sync(kFullMask, my_goff, (first[q] + e + 1) & 31);
+            acc_t t0 = 1, t1 = 1;
+            if (MEAN) {
+              t0 = __shfl_sync(kFullMask, my_scale, (first[q] + e) & 31);
+              t1 = __shfl_sync(kFullMask, my_scale, (first[q] + e + 1) & 31);
+            }
+            Raw<VB> r0[VPL], r1[VPL];
+#pragma unroll
+            for (int j = 0; j < VPL; ++j) {
+              r0[j] = raw_zero<VB>();
+              r1[j] = raw_zero<VB>();
+              if (e < len[q]) r0[j] = ld_stream_hint<VB>(grad_ptr(o0, j), keep);
+              if (e + 1 < len[q]) r1[j] = ld_stream_hint<VB>(grad_ptr(o1, j), keep);
+            }
+#pragma unroll
+            for (int j = 0; j < VPL; ++j) {
+              add_grad<T, VB, MEAN>(r0[j], t0, acc[j]);
+              add_grad<T, VB, MEAN>(r1[j], t1, acc[j]);
+            }
+          }
+        }
+        for (int p = tail_lo[q]; p < tail_hi[q]; p += 2) {  // group-uniform; entries behind the tile
+          acc_t t0 = 1, t1 = 1;
+          const bool two = p + 1 < tail_hi[q];
+          const uint32_t o0 = grad_units(static_cast<uint32_t>(__ldg(vals + p)), &t0);
+          const uint32_t o1 = two ? grad_units(static_cast<uint32_t>(__ldg(vals + p + 1)), &t1) : o0;
+          Raw<VB> r0[VPL], r1[VPL];
+#pragma unroll
+          for (int j = 0; j < VPL; ++j) {
+            r0[j] = ld_stream_hint<VB>(grad_ptr(o0, j), keep);
+            r1[j] = raw_zero<VB>();
+            if (two) r1[j] = ld_stream_hint<VB>(grad_ptr(o1, j), keep);
+          }
+#pragma unroll
+          for (int j = 0; j < VPL; ++j) {
+            add_grad<T, VB, MEAN>(r0[j], t0, acc[j]);
+            add_grad<T, VB, MEAN>(r1[j], t1, acc[j]);
+          }
+        }
+        acc_t mult = static_cast<acc_t>(a.lr);
+        if (OPT == kExactAdagrad) {
+          acc_t part = 0;
+#pragma unroll
+          for (int j = 0; j < VPL; ++j) {
+            if (vact[j]) part += sq_sum(acc[j], NE);
+          }
+          const acc_t g2 = group_sum(part, lpr_log2);
+          const float st = st_old[q] + static_cast<float>(g2);
+          if (has[q] && sub == 0) a.state[wid[q]] = st;
+          mult = static_cast<acc_t>(a.lr * (1.0f / (sqrtf(st) + a.eps)));
+        }
+        char* wrow = wbase + static_cast<uint64_t>(wid[q]) * row_bytes;
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+          if (has[q] && vact[j]) apply_update<T, VB, SR>(wrow + voff[j], wraw[q][j], acc[j], mult, &rng, streaming);
+        }
       }
     }
-    const int maxlen = __reduce_max_sync(kFullMask, len);
-    char* wrow = static_cast<char*>(a.weights) + static_cast<int64_t>(row) * row_bytes;
 
-    acc_t g2 = 0;
-    if (OPT == kExactAdagrad && a.nchunks > 1) {
+    tile = ntile;
+    if (tile >= ntiles) break;
+    cur = nxt;
+  }
+}
+
+// Rows wider than 32 vectors: one run per lane group at a time, the row is walked in chunks of 32
+// vectors (twice for rowwise Adagrad, whose step size needs the whole row's gradient norm first).
+template <typename T, int VB, int OPT, bool MEAN, bool SR>
+__global__ void __launch_bounds__(kBwdThreads) run_kernel_wide(const BwdArgs a) {
+  using acc_t = typename Acc<T>::type;
+  constexpr int NE = VB / sizeof(T);
+  const int lane = threadIdx.x & 31;
+  const int lpr_log2 = a.lpr1_log2;
+  const int gpw = 32 >> lpr_log2;  // lane groups (= concurrent runs) per warp
+  const int sub = lane & ((1 << lpr_log2) - 1);
+  const int slot = lane >> lpr_log2;
+  const int N = a.N;
+  const int64_t ntiles = (static_cast<int64_t>(N) + 31) >> 5;
+  const int64_t wstride = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  int64_t tile = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (tile >= ntiles) return;
+  const int64_t row_bytes = static_cast<int64_t>(a.D) * sizeof(T);
+  const uint32_t* __restrict__ keys = a.keys;
+  const int32_t* __restrict__ vals = a.vals;
+  Philox rng(a.sr_seed, static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x, a.sr_offset);
+
+  const uint64_t keep = l2_policy_evict_last(), streaming = l2_policy_evict_first();
+  // A tile's registers: key/val of entry p0+lane, and a halo word: lane 0 holds the key before the
+  // tile, lane 31 the key after it.
+  auto load_tile = [&](int64_t tl, uint32_t& key, int32_t& val, uint32_t& halo) {
+    const int64_t p = (tl << 5) + lane;
+    key = 0xffffffffu;
+    val = 0;
+    halo = 0xffffffffu;
+    if (p < N) {
+      key = __ldg(keys + p);
+      val = __ldg(vals + p);
+    }
+    if (lane == 0 && p > 0) halo = __ldg(keys + p - 1);
+    if (lane == 31 && p + 1 < N) halo = __ldg(keys + p + 1);
+  };
+
+  uint32_t key, halo;
+  int32_t val;
+  load_tile(tile, key, val, halo);
+
+  while (true) {
+    const int64_t ntile = tile + wstride;
+    uint32_t nkey = 0, nhalo = 0;
+    int32_t nval = 0;
+    if (ntile < ntiles) load_tile(ntile, nkey, nval, nhalo);
+
+    const int p0 = static_cast<int>(tile << 5);
+    const int nvalid = min(32, N - p0);
+    uint32_t prev = __shfl_up_sync(kFullMask, key, 1);
+    if (lane == 0) prev = halo;
+    const bool is_start = lane < nvalid && (p0 + lane == 0 || key != prev);
+    const unsigned smask = __ballot_sync(kFullMask, is_start);
+    const int nstarts = __popc(smask);
+    const uint32_t after = __shfl_sync(kFullMask, halo, 31);  // key following the tile (if any)
+    const bool more_after = p0 + 32 < N;
+
+    for (int k = 0; k < nstarts; k += gpw) {
+      const int n = k + slot;
+      bool has = n < nstarts;
+      const int i = has ? static_cast<int>(__fns(smask, 0, n + 1)) : 0;
+      const unsigned rest = (i >= 31) ? 0u : (smask & ~((2u << i) - 1u));
+      const int j = rest ? (__ffs(rest) - 1) : nvalid;
+      int len = has ? (j - i) : 0;
+      const uint32_t row = __shfl_sync(kFullMask, key, i);
+      // does the run continue behind the tile?
+      int tail_lo = 0, tail_hi = 0;
+      if (has && j == 32 && more_after && after == row) {
+        tail_lo = p0 + 32;
+        tail_hi = run_end(keys, tail_lo + 1, N, row);
+        if (len + (tail_hi - tail_lo) > a.long_threshold) {
+          if (sub == 0) a.long_list[atomicAdd(a.long_count, 1)] = make_int2(p0 + i, tail_hi);
+          has = false;
+          len = 0;
+          tail_hi = tail_lo;
+        }
+      }
+      const int maxlen = __reduce_max_sync(kFullMask, len);
+      const uint32_t wrow_id = has ? key_to_row(a, row) : 0u;
+      char* wrow = static_cast<char*>(a.weights) + static_cast<int64_t>(wrow_id) * row_bytes;
+
+      // sums vector v of the run's gradient rows into acc (tile part with shuffled bag ids, then the tail)
+      auto accumulate = [&](int v, bool vact, acc_t* acc) {
+        for (int e = 0; e < maxlen; e += 2) {
+          const uint32_t bag0 = static_cast<uint32_t>(__shfl_sync(kFullMask, val, (i + e) & 31));
+          const uint32_t bag1 = static_cast<uint32_t>(__shfl_sync(kFullMask, val, (i + e + 1) & 31));
+          Raw<VB> r0 = raw_zero<VB>(), r1 = raw_zero<VB>();
+          acc_t s0 = 1, s1 = 1;
+          if (e < len && vact) r0 = load_grad<T, VB, MEAN>(a, bag0, v, keep, &s0);
+          if (e + 1 < len && vact) r1 = load_grad<T, VB, MEAN>(a, bag1, v, keep, &s1);
+          add_grad<T, VB, MEAN>(r0, s0, acc);
+          add_grad<T, VB, MEAN>(r1, s1, acc);
+        }
+        for (int q = tail_lo; q < tail_hi; ++q) {  // group-uniform, rare
+          acc_t s0 = 1;
+          Raw<VB> r0 = raw_zero<VB>();
+          if (vact) r0 = load_grad<T, VB, MEAN>(a, static_cast<uint32_t>(__ldg(vals + q)), v, keep, &s0);
+          add_grad<T, VB, MEAN>(r0, s0, acc);
+        }
+      };
+
+      acc_t g2 = 0;
+      if (OPT == kExactAdagrad && a.nchunks > 1) {
+        for (int c = 0; c < a.nchunks; ++c) {
+          const int v = (c << 5) + sub;
+          acc_t acc[NE];
+#pragma unroll
+          for (int kk = 0; kk < NE; ++kk) acc[kk] = 0;
+          accumulate(v, v < a.nvec, acc);
+          g2 += sq_sum(acc, NE);
+        }
+        g2 = group_sum(g2, lpr_log2);
+      }
+      acc_t mult = static_cast<acc_t>(a.lr);
       for (int c = 0; c < a.nchunks; ++c) {
         const int v = (c << 5) + sub;
         const bool vact = v < a.nvec;
+        Raw<VB> wraw = raw_zero<VB>();
+        if (has && vact) wraw = ld_rw<VB>(wrow + static_cast<int64_t>(v) * VB);
         acc_t acc[NE];
 #pragma unroll
-        for (int k = 0; k < NE; ++k) acc[k] = 0;
-        sum_grads<T, VB, MEAN, UNROLL>(a, s, len, 0, 1, maxlen, v, vact, acc);
-        g2 += sq_sum(acc, NE);
+        for (int kk = 0; kk < NE; ++kk) acc[kk] = 0;
+        accumulate(v, vact, acc);
+        if (OPT == kExactAdagrad && c == 0) {
+          if (a.nchunks == 1) g2 = group_sum(sq_sum(acc, NE), lpr_log2);
+          const float st = (has ? a.state[wrow_id] : 0.f) + static_cast<float>(g2);
+          __syncwarp();
+          if (has && sub == 0) a.state[wrow_id] = st;
+          mult = static_cast<acc_t>(a.lr * (1.0f / (sqrtf(st) + a.eps)));
+        }
+        if (has && vact) apply_update<T, VB, SR>(wrow + static_cast<int64_t>(v) * VB, wraw, acc, mult, &rng, streaming);
       }
-      g2 = group_sum(g2, lpr_log2);
     }
-    acc_t mult = static_cast<acc_t>(a.lr);
-    for (int c = 0; c < a.nchunks; ++c) {
-      const int v = (c << 5) + sub;
-      const bool vact = v < a.nvec;
-      Raw<VB> wraw = raw_zero<VB>();
-      if (has && vact) wraw = ld_rw<VB>(wrow + static_cast<int64_t>(v) * VB);
-      acc_t acc[NE];
-#pragma unroll
-      for (int k = 0; k < NE; ++k) acc[k] = 0;
-      sum_grads<T, VB, MEAN, UNROLL>(a, s, len, 0, 1, maxlen, v, vact, acc);
-      if (OPT == kExactAdagrad && c == 0) {
-        if (a.nchunks == 1) g2 = group_sum(sq_sum(acc, NE), lpr_log2);
-        const float st = (has ? a.state[row] : 0.f) + static_cast<float>(g2);
-        __syncwarp();
-        if (has && sub == 0) a.state[row] = st;
-        mult = static_cast<acc_t>(a.lr * (1.0f / (sqrtf(st) + a.eps)));
-      }
-      if (has && vact) apply_update<T, VB, SR>(wrow + static_cast<int64_t>(v) * VB, wraw, acc, mult, &rng);
-    }
+
+    tile = ntile;
+    if (tile >= ntiles) break;
+    key = nkey;
+    val = nval;
+    halo = nhalo;
   }
 }
 
 // One CTA per queued long run.
 template <typename T, int VB, int OPT, bool MEAN, bool SR>
-__global__ void __launch_bounds__(kBwdThreads) long_segment_kernel(const BwdArgs a) {
+__global__ void __launch_bounds__(kBwdThreads) long_run_kernel(const BwdArgs a) {
   using acc_t = typename Acc<T>::type;
   constexpr int NE = VB / sizeof(T);
   __shared__ acc_t part[kBwdThreads * NE];
   const int lane = threadIdx.x & 31;
-  const int lpr_log2 = a.lpr_log2;
+  const int lpr_log2 = a.lpr1_log2;
   const int lpr = 1 << lpr_log2;
   const int sub = lane & (lpr - 1);
   const int gid = threadIdx.x >> lpr_log2;
   const int groups = blockDim.x >> lpr_log2;
-  const int U = __ldg(a.counters);
-  const int nlong = __ldg(a.counters + 1);
+  const int nlong = *a.long_count;
   const int64_t row_bytes = static_cast<int64_t>(a.D) * sizeof(T);
-  Philox rng(a.sr_seed, (static_cast<uint64_t>(gridDim.x) + 1 + blockIdx.x) * blockDim.x + threadIdx.x + (1ull << 40),
-             a.sr_offset);
+  Philox rng(a.sr_seed, (1ull << 40) + static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x, a.sr_offset);
+  const uint64_t keep = l2_policy_evict_last(), streaming = l2_policy_evict_first();
 
   for (int li = blockIdx.x; li < nlong; li += gridDim.x) {
-    const int seg = a.long_list[li];
-    const int s = __ldg(a.seg_starts + seg);
-    const int e = (seg + 1 < U) ? __ldg(a.seg_starts + seg + 1) : a.N;
-    const int len = e - s;
-    const uint32_t row = __ldg(a.sorted_rows + s);
+    const int2 run = a.long_list[li];
+    const int s = run.x, len = run.y - run.x;
+    const uint32_t row = key_to_row(a, __ldg(a.keys + s));
     char* wrow = static_cast<char*>(a.weights) + static_cast<int64_t>(row) * row_bytes;
-    const int iters = (len + groups - 1) / groups;  // block-uniform
 
-    // Folds the groups' partial sums for vector v in group order; every thread of warp 0 returns
-    // the total of its own `sub`, other warps return garbage they never use.
+    // Folds the groups' partial sums for chunk c in group order; every thread of warp 0 ends with the
+    // total of its own `sub`.
     auto reduce_chunk = [&](int c, acc_t* total) {
       const int v = (c << 5) + sub;
       const bool vact = v < a.nvec;
       acc_t acc[NE];
 #pragma unroll
       for (int k = 0; k < NE; ++k) acc[k] = 0;
-      sum_grads<T, VB, MEAN, 4>(a, s, len, gid, groups, iters, v, vact, acc);
+      for (int i = gid; i < len; i += groups * 4) {  // four gradient rows in flight per lane
+        uint32_t bag[4];
+        Raw<VB> r[4];
+        acc_t sc[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int iu = i + u * groups;
+          bag[u] = iu < len ? static_cast<uint32_t>(__ldg(a.vals + s + iu)) : 0u;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          r[u] = raw_zero<VB>();
+          sc[u] = 1;
+          if (i + u * groups < len && vact) r[u] = load_grad<T, VB, MEAN>(a, bag[u], v, keep, &sc[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) add_grad<T, VB, MEAN>(r[u], sc[u], acc);
+      }
       __syncthreads();  // previous use of `part` finished
 #pragma unroll
       for (int k = 0; k < NE; ++k) part[threadIdx.x * NE + k] = acc[k];
@@ -442,57 +778,79 @@ __global__ void __launch_bounds__(kBwdThreads) long_segment_kernel(const BwdArgs
         }
         if (gid == 0 && vact) {
           const Raw<VB> wraw = ld_rw<VB>(wrow + static_cast<int64_t>(v) * VB);
-          apply_update<T, VB, SR>(wrow + static_cast<int64_t>(v) * VB, wraw, tot, mult, &rng);
+          apply_update<T, VB, SR>(wrow + static_cast<int64_t>(v) * VB, wraw, tot, mult, &rng, streaming);
         }
       }
     }
   }
 }
 
+// The run_kernel instance for (SEGS, VPL); only 16-byte-vector fp16/fp32 rows get VPL > 1.
 template <typename T, int VB, int OPT, bool MEAN, bool SR>
-int launch_segments(const BwdArgs& a, cudaStream_t stream) {
+void (*pick_run_kernel(int segs, int vpl))(const BwdArgs) {
+  if constexpr (VB == 16 && sizeof(T) <= 4) {
+    if (vpl == 4) return segs == 2 ? run_kernel<T, VB, OPT, MEAN, SR, 2, 4> : run_kernel<T, VB, OPT, MEAN, SR, 1, 4>;
+    if (vpl == 2) return segs == 2 ? run_kernel<T, VB, OPT, MEAN, SR, 2, 2> : run_kernel<T, VB, OPT, MEAN, SR, 1, 2>;
+  }
+  return segs == 2 ? run_kernel<T, VB, OPT, MEAN, SR, 2, 1> : run_kernel<T, VB, OPT, MEAN, SR, 1, 1>;
+}
+
+template <typename T, int VB, int OPT, bool MEAN, bool SR>
+int launch_runs(const BwdArgs& a, cudaStream_t stream) {
   int threads = tuning(kTuneBwdThreads);
   if (threads <= 0) threads = kBwdThreads;
   if (threads > kBwdThreads || threads % 32 != 0)
     return fail(TBE_ERR_INVALID_ARGUMENT, "bwd_threads must be a multiple of 32 <= %d", kBwdThreads);
-  const int unroll = tuning(kTuneBwdUnroll) > 0 ? tuning(kTuneBwdUnroll) : 2;
   void (*kernel)(const BwdArgs) = nullptr;
-  switch (unroll) {
-    case 1: kernel = segment_kernel<T, VB, OPT, MEAN, SR, 1>; break;
-    case 2: kernel = segment_kernel<T, VB, OPT, MEAN, SR, 2>; break;
-    case 4: kernel = segment_kernel<T, VB, OPT, MEAN, SR, 4>; break;
-    default: return fail(TBE_ERR_INVALID_ARGUMENT, "bwd_unroll must be 1, 2 or 4");
+  BwdArgs args = a;
+  // vectors per lane: the most that divides the row, unless a knob says otherwise
+  // (two per lane measured best on B200 for 256- and 512-byte rows; four costs too many registers)
+  const int vpl_max = (VB != 16 || sizeof(T) == 8) ? 1 : (a.nvec % 4 == 0) ? 4 : (a.nvec % 2 == 0) ? 2 : 1;
+  int vpl = vpl_max < 2 ? vpl_max : 2;
+  const int knob = tuning(kTuneBwdVpl);
+  if ((knob == 1 || knob == 2 || knob == 4) && knob <= vpl_max) vpl = knob;
+  const int lanes_needed = (a.nvec + vpl - 1) / vpl;
+  if (lanes_needed > 32) {
+    kernel = run_kernel_wide<T, VB, OPT, MEAN, SR>;
+  } else {
+    int l = 0;
+    while ((1 << l) < lanes_needed) ++l;
+    args.lpr_log2 = l;
+    const int segs = tuning(kTuneBwdUnroll) > 0 ? tuning(kTuneBwdUnroll) : (vpl == 1 ? 2 : 1);
+    if (segs != 1 && segs != 2) return fail(TBE_ERR_INVALID_ARGUMENT, "bwd_unroll must be 1 or 2");
+    kernel = pick_run_kernel<T, VB, OPT, MEAN, SR>(segs, vpl);
   }
   int per_sm = 0;
   TBE_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0));
   if (per_sm < 1) per_sm = 1;
-  const int gpw = 32 >> a.lpr_log2;
-  const int64_t groups_per_block = static_cast<int64_t>(threads / 32) * gpw;
-  int64_t blocks = (static_cast<int64_t>(a.N) + groups_per_block - 1) / groups_per_block;  // U <= N
+  if (tuning(kTuneBwdBlocksPerSM) > 0 && tuning(kTuneBwdBlocksPerSM) < per_sm) per_sm = tuning(kTuneBwdBlocksPerSM);
+  const int64_t ntiles = (static_cast<int64_t>(a.N) + 31) / 32;
+  const int wpb = threads / 32;
+  int64_t blocks = (ntiles + wpb - 1) / wpb;
   const int64_t resident = static_cast<int64_t>(device_sm_count()) * per_sm;
   if (blocks > resident) blocks = resident;
   if (blocks < 1) blocks = 1;
   {
-    KernelTimer timer("segment_kernel", stream);
-    kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(a);
+    KernelTimer timer("run_kernel", stream);
+    kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(args);
   }
-  TBE_CHECK_LAUNCH("segment_kernel");
+  TBE_CHECK_LAUNCH("run_kernel");
   {
-    KernelTimer timer("long_segment_kernel", stream);
-    long_segment_kernel<T, VB, OPT, MEAN, SR><<<device_sm_count() * 2, kBwdThreads, 0, stream>>>(a);
+    KernelTimer timer("long_run_kernel", stream);
+    long_run_kernel<T, VB, OPT, MEAN, SR><<<device_sm_count() * 2, kBwdThreads, 0, stream>>>(a);
   }
-  TBE_CHECK_LAUNCH("long_segment_kernel");
+  TBE_CHECK_LAUNCH("long_run_kernel");
   return TBE_OK;
 }
 
 template <typename T, int VB, int OPT>
 int dispatch_flags(const BwdArgs& a, bool mean, bool sr, cudaStream_t stream) {
   if (mean) {
-    if (sr) return launch_segments<T, VB, OPT, true, true>(a, stream);
-    return launch_segments<T, VB, OPT, true, false>(a, stream);
+    if (sr) return launch_runs<T, VB, OPT, true, true>(a, stream);
+    return launch_runs<T, VB, OPT, true, false>(a, stream);
   }
-  if (sr) return launch_segments<T, VB, OPT, false, true>(a, stream);
-  return launch_segments<T, VB, OPT, false, false>(a, stream);
+  if (sr) return launch_runs<T, VB, OPT, false, true>(a, stream);
+  return launch_runs<T, VB, OPT, false, false>(a, stream);
 }
 
 template <int OPT>
@@ -509,42 +867,52 @@ int dispatch_bwd(const BwdArgs& a, int dtype, int vb, bool mean, bool sr, cudaSt
   return fail(TBE_ERR_INVALID_ARGUMENT, "unknown dtype %d", dtype);
 }
 
-int check_common(const char* who, const void* grad, const void* weights, const int32_t* table_offsets,
-                 const int32_t* indices, const int32_t* offsets, int64_t T, int64_t B, int64_t D, int64_t N,
-                 int64_t total_rows, int dtype, const void* workspace) {
-  TBE_REQUIRE(grad && weights && table_offsets && indices && offsets, "%s: null pointer argument", who);
-  TBE_REQUIRE(workspace != nullptr, "%s: workspace is null", who);
+int check_sizes(const char* who, int64_t T, int64_t B, int64_t N, int64_t total_rows) {
   TBE_REQUIRE(T > 0 && B > 0, "%s: T and B must be > 0", who);
-  TBE_REQUIRE(D > 0 && D % 4 == 0, "%s: D must be a positive multiple of 4 (got %lld)", who, (long long)D);
-  TBE_REQUIRE(N >= 0 && N < (1ll << 31) - 1, "%s: N out of range", who);
+  TBE_REQUIRE(N >= 0 && N < (1ll << 31) - 64, "%s: N out of range", who);
   TBE_REQUIRE(T * B < (1ll << 31), "%s: B*T out of range", who);
   TBE_REQUIRE(total_rows > 0 && total_rows < (1ll << 31), "%s: total_rows out of range", who);
-  TBE_REQUIRE(dtype == TBE_F32 || dtype == TBE_F16 || dtype == TBE_F64, "%s: bad dtype %d", who, dtype);
+  return TBE_OK;
+}
+
+int prepare_workspace(const char* who, void* workspace, int64_t workspace_bytes, int64_t N, int64_t total_rows,
+                      Workspace* ws) {
+  TBE_REQUIRE(workspace != nullptr, "%s: workspace is null", who);
+  TBE_REQUIRE(reinterpret_cast<uintptr_t>(workspace) % 256 == 0, "%s: workspace must be 256-byte aligned", who);
+  const int rc = carve(workspace, N, total_rows, ws);
+  if (rc != TBE_OK) return rc;
+  if (static_cast<int64_t>(ws->total) > workspace_bytes)
+    return fail(TBE_ERR_WORKSPACE_TOO_SMALL, "%s: workspace has %lld bytes, %lld needed", who,
+                (long long)workspace_bytes, (long long)ws->total);
   return TBE_OK;
 }
 
 int exact_backward(int opt, const void* grad, int64_t stride_b, int64_t stride_t, void* weights,
                    const int32_t* table_offsets, const int32_t* indices, const int32_t* offsets, float* state,
                    int64_t T, int64_t B, int64_t D, int64_t N, int64_t total_rows, int dtype, int pooling,
-                   float lr, float eps, int sr, uint64_t sr_seed, uint64_t sr_offset, void* workspace,
-                   int64_t workspace_bytes, void* stream_v) {
+                   float lr, float eps, int sr, uint64_t sr_seed, uint64_t sr_offset, int64_t max_rows_per_table,
+                   int plan_ready, void* workspace, int64_t workspace_bytes, void* stream_v) {
   const char* who = opt == kSGD ? "tbe_backward_sgd" : "tbe_backward_exact_rowwise_adagrad";
-  int rc = check_common(who, grad, weights, table_offsets, indices, offsets, T, B, D, N, total_rows, dtype, workspace);
+  TBE_REQUIRE(grad && weights && table_offsets && offsets && (indices || N == 0), "%s: null pointer argument", who);
+  int rc = check_sizes(who, T, B, N, total_rows);
   if (rc != TBE_OK) return rc;
+  TBE_REQUIRE(D > 0 && D % 4 == 0, "%s: D must be a positive multiple of 4 (got %lld)", who, (long long)D);
+  TBE_REQUIRE(dtype == TBE_F32 || dtype == TBE_F16 || dtype == TBE_F64, "%s: bad dtype %d", who, dtype);
   TBE_REQUIRE(pooling == TBE_POOL_SUM || pooling == TBE_POOL_MEAN, "%s: bad pooling %d", who, pooling);
   TBE_REQUIRE(opt == kSGD || state != nullptr, "%s: optimizer_state is null", who);
+  TBE_REQUIRE(stride_b >= 0 && stride_t >= 0 && stride_b * 8 < (1ll << 32) && stride_t * 8 < (1ll << 32),
+              "%s: grad_output strides must be non-negative and below 2^29 elements", who);
+  Workspace ws;
+  rc = prepare_workspace(who, workspace, workspace_bytes, N, total_rows, &ws);
+  if (rc != TBE_OK) return rc;
   if (N == 0) return TBE_OK;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  Workspace ws;
-  rc = carve(workspace, N, total_rows, &ws);
-  if (rc != TBE_OK) return rc;
-  if (static_cast<int64_t>(ws.total) > workspace_bytes)
-    return fail(TBE_ERR_WORKSPACE_TOO_SMALL, "%s: workspace has %lld bytes, %lld needed", who,
-                (long long)workspace_bytes, (long long)ws.total);
-  TBE_REQUIRE(reinterpret_cast<uintptr_t>(workspace) % 256 == 0, "%s: workspace must be 256-byte aligned", who);
-  Plan plan;
-  rc = build_plan(table_offsets, indices, offsets, T, B, N, total_rows, false, ws, &plan, stream);
-  if (rc != TBE_OK) return rc;
+  const KeyLayout layout = key_layout(T, total_rows, max_rows_per_table, false);
+  if (!plan_ready) {
+    rc = build_plan(table_offsets, indices, offsets, T, B, N, layout, ws, stream);
+    if (rc != TBE_OK) return rc;
+  }
+  TBE_CUDA_TRY(cudaMemsetAsync(ws.counters, 0, 64, stream));
 
   BwdArgs a{};
   a.grad = grad;
@@ -552,26 +920,28 @@ int exact_backward(int opt, const void* grad, int64_t stride_b, int64_t stride_t
   a.stride_t = stride_t;
   a.weights = weights;
   a.state = state;
-  a.sorted_rows = plan.sorted_rows;
-  a.sorted_vals = plan.sorted_vals;
-  a.seg_starts = ws.seg_starts;
-  a.counters = ws.counters;
+  a.keys = ws.keys;
+  a.vals = ws.vals;
   a.long_list = ws.long_list;
   a.long_count = ws.counters + 1;
   a.offsets = offsets;
+  a.table_offsets = table_offsets;
+  a.idx_bits = layout.idx_bits;
+  a.divB = make_fastdiv(static_cast<uint32_t>(B));
   a.B = static_cast<int32_t>(B);
   a.D = static_cast<int32_t>(D);
   a.N = static_cast<int32_t>(N);
   const int es = elem_size(dtype);
   // the gradient rows must allow the same vector width as the weight rows
-  const bool grad16 = reinterpret_cast<uintptr_t>(grad) % 16 == 0 && (stride_b * es) % 16 == 0 && (stride_t * es) % 16 == 0;
+  const bool grad16 =
+      reinterpret_cast<uintptr_t>(grad) % 16 == 0 && (stride_b * es) % 16 == 0 && (stride_t * es) % 16 == 0;
   const RowGeom g = make_geom(D, dtype, weights, grad16 ? nullptr : reinterpret_cast<const void*>(uintptr_t(8)));
   TBE_REQUIRE(g.vb == 16 || dtype == TBE_F16, "%s: weights and grad_output rows must be 16-byte aligned", who);
   if (g.vb == 8)
     TBE_REQUIRE(reinterpret_cast<uintptr_t>(grad) % 8 == 0 && (stride_b * es) % 8 == 0 && (stride_t * es) % 8 == 0 &&
                     reinterpret_cast<uintptr_t>(weights) % 8 == 0,
                 "%s: weights and grad_output rows must be 8-byte aligned", who);
-  a.lpr_log2 = g.lpr_log2;
+  a.lpr1_log2 = g.lpr_log2;
   a.nvec = g.nvec;
   a.nchunks = g.nchunks;
   a.long_threshold = tuning(kTuneLongSegment) > 0 ? tuning(kTuneLongSegment) : kDefaultLongSegment;
@@ -596,13 +966,30 @@ extern "C" int64_t tbe_backward_workspace_bytes(int64_t N, int64_t total_rows) {
   return static_cast<int64_t>(ws.total);
 }
 
+extern "C" int tbe_backward_plan(const int32_t* table_offsets, const int32_t* indices, const int32_t* offsets,
+                                 int64_t T, int64_t B, int64_t N, int64_t total_rows,
+                                 int64_t max_rows_per_table, void* workspace, int64_t workspace_bytes,
+                                 void* stream) {
+  using namespace tbe;
+  const char* who = "tbe_backward_plan";
+  TBE_REQUIRE(table_offsets && offsets && (indices || N == 0), "%s: null pointer argument", who);
+  int rc = check_sizes(who, T, B, N, total_rows);
+  if (rc != TBE_OK) return rc;
+  Workspace ws;
+  rc = prepare_workspace(who, workspace, workspace_bytes, N, total_rows, &ws);
+  if (rc != TBE_OK || N == 0) return rc;
+  return build_plan(table_offsets, indices, offsets, T, B, N, key_layout(T, total_rows, max_rows_per_table, false), ws,
+                    static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int tbe_backward_sgd(const void* grad_output, int64_t stride_b, int64_t stride_t, void* weights,
                                 const int32_t* table_offsets, const int32_t* indices, const int32_t* offsets,
                                 int64_t T, int64_t B, int64_t D, int64_t N, int64_t total_rows, int dtype,
-                                int pooling, float lr, void* workspace, int64_t workspace_bytes, void* stream) {
+                                int pooling, float lr, int64_t max_rows_per_table, int plan_ready, void* workspace,
+                                int64_t workspace_bytes, void* stream) {
   return tbe::exact_backward(tbe::kSGD, grad_output, stride_b, stride_t, weights, table_offsets, indices, offsets,
-                             nullptr, T, B, D, N, total_rows, dtype, pooling, lr, 0.f, 0, 0, 0, workspace,
-                             workspace_bytes, stream);
+                             nullptr, T, B, D, N, total_rows, dtype, pooling, lr, 0.f, 0, 0, 0, max_rows_per_table,
+                             plan_ready, workspace, workspace_bytes, stream);
 }
 
 extern "C" int tbe_backward_exact_rowwise_adagrad(const void* grad_output, int64_t stride_b, int64_t stride_t,
@@ -611,11 +998,12 @@ extern "C" int tbe_backward_exact_rowwise_adagrad(const void* grad_output, int64
                                                   float* optimizer_state, int64_t T, int64_t B, int64_t D,
                                                   int64_t N, int64_t total_rows, int dtype, int pooling, float lr,
                                                   float eps, int stochastic_rounding, uint64_t sr_seed,
-                                                  uint64_t sr_offset, void* workspace, int64_t workspace_bytes,
-                                                  void* stream) {
+                                                  uint64_t sr_offset, int64_t max_rows_per_table, int plan_ready,
+                                                  void* workspace, int64_t workspace_bytes, void* stream) {
   return tbe::exact_backward(tbe::kExactAdagrad, grad_output, stride_b, stride_t, weights, table_offsets, indices,
                              offsets, optimizer_state, T, B, D, N, total_rows, dtype, pooling, lr, eps,
-                             stochastic_rounding, sr_seed, sr_offset, workspace, workspace_bytes, stream);
+                             stochastic_rounding, sr_seed, sr_offset, max_rows_per_table, plan_ready, workspace,
+                             workspace_bytes, stream);
 }
 
 extern "C" int tbe_sort_segments(const int32_t* table_offsets, const int32_t* indices, const int32_t* offsets,
@@ -623,28 +1011,32 @@ extern "C" int tbe_sort_segments(const int32_t* table_offsets, const int32_t* in
                                  int32_t* sorted_bags, int32_t* segment_starts, int32_t* num_segments,
                                  void* workspace, int64_t workspace_bytes, void* stream_v) {
   using namespace tbe;
-  TBE_REQUIRE(table_offsets && indices && offsets && sorted_rows && sorted_bags && segment_starts && num_segments &&
-                  workspace,
-              "tbe_sort_segments: null pointer argument");
-  TBE_REQUIRE(T > 0 && B > 0 && N >= 0 && N < (1ll << 31) - 1 && total_rows > 0 && total_rows < (1ll << 31),
-              "tbe_sort_segments: sizes out of range");
+  const char* who = "tbe_sort_segments";
+  TBE_REQUIRE(table_offsets && offsets && (indices || N == 0) && sorted_rows && sorted_bags && segment_starts &&
+                  num_segments,
+              "%s: null pointer argument", who);
+  int rc = check_sizes(who, T, B, N, total_rows);
+  if (rc != TBE_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  Workspace ws;
+  rc = prepare_workspace(who, workspace, workspace_bytes, N, total_rows, &ws);
+  if (rc != TBE_OK) return rc;
   if (N == 0) {
     TBE_CUDA_TRY(cudaMemsetAsync(num_segments, 0, 4, stream));
-    TBE_CUDA_TRY(cudaMemsetAsync(segment_starts, 0, 4, stream));
     return TBE_OK;
   }
-  Workspace ws;
-  int rc = carve(workspace, N, total_rows, &ws);
+  rc = build_plan(table_offsets, indices, offsets, T, B, N, key_layout(T, total_rows, 0, true), ws, stream);
   if (rc != TBE_OK) return rc;
-  if (static_cast<int64_t>(ws.total) > workspace_bytes)
-    return fail(TBE_ERR_WORKSPACE_TOO_SMALL, "tbe_sort_segments: workspace has %lld bytes, %lld needed",
-                (long long)workspace_bytes, (long long)ws.total);
-  Plan plan;
-  rc = build_plan(table_offsets, indices, offsets, T, B, N, total_rows, false, ws, &plan, stream);
-  if (rc != TBE_OK) return rc;
-  TBE_CUDA_TRY(cudaMemcpyAsync(sorted_rows, plan.sorted_rows, N * 4, cudaMemcpyDeviceToDevice, stream));
-  TBE_CUDA_TRY(cudaMemcpyAsync(sorted_bags, plan.sorted_vals, N * 4, cudaMemcpyDeviceToDevice, stream));
+  size_t bytes = ws.cub_bytes;
+  thrust::counting_iterator<int32_t> it(0);
+  {
+    KernelTimer timer("cub_select_run_starts", stream);
+    TBE_CUDA_TRY(cub::DeviceSelect::If(ws.cub_temp, bytes, it, ws.seg_starts, ws.counters, static_cast<int64_t>(N),
+                                       RunStart{ws.keys}, stream));
+  }
+  count_library_launch();
+  TBE_CUDA_TRY(cudaMemcpyAsync(sorted_rows, ws.keys, N * 4, cudaMemcpyDeviceToDevice, stream));
+  TBE_CUDA_TRY(cudaMemcpyAsync(sorted_bags, ws.vals, N * 4, cudaMemcpyDeviceToDevice, stream));
   TBE_CUDA_TRY(cudaMemcpyAsync(segment_starts, ws.seg_starts, N * 4, cudaMemcpyDeviceToDevice, stream));
   TBE_CUDA_TRY(cudaMemcpyAsync(num_segments, ws.counters, 4, cudaMemcpyDeviceToDevice, stream));
   return TBE_OK;

@@ -23,7 +23,17 @@ int fail(int code, const char* fmt, ...);
 void count_kernel_launch(int n = 1);
 void count_library_launch(int n = 1);
 int tuning(int which);  // see tbe_api.cu
-enum Tuning { kTuneFwdUnroll = 0, kTuneFwdThreads, kTuneBwdThreads, kTuneBwdUnroll, kTuneLongSegment, kTuneCount };
+enum Tuning {
+  kTuneFwdUnroll = 0,
+  kTuneFwdThreads,
+  kTuneBwdThreads,
+  kTuneBwdUnroll,
+  kTuneLongSegment,
+  kTuneFwdBlocksPerSM,
+  kTuneBwdBlocksPerSM,
+  kTuneBwdVpl,
+  kTuneCount
+};
 
 #define TBE_CUDA_TRY(expr)                                                            \
   do {                                                                                \
@@ -168,6 +178,101 @@ __device__ __forceinline__ void st_row<16>(void* p, const Raw<16>& r) {
 template <>
 __device__ __forceinline__ void st_row<8>(void* p, const Raw<8>& r) {
   asm volatile("st.global.v2.u32 [%0], {%1,%2};" : : "l"(p), "r"(r.w[0]), "r"(r.w[1]) : "memory");
+}
+
+// L2 residency hints.  Gather/scatter kernels stream gigabytes of table rows once through L2 while
+// re-reading a few tens of megabytes (pooled gradient rows, sorted ids) many times: the streamed
+// rows are marked evict-first and the re-read rows evict-last so the latter stay resident.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_normal() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+
+template <int VB>
+__device__ __forceinline__ Raw<VB> ld_stream_hint(const void* p, uint64_t policy);
+template <>
+__device__ __forceinline__ Raw<16> ld_stream_hint<16>(const void* p, uint64_t policy) {
+  Raw<16> r;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+               : "=r"(r.w[0]), "=r"(r.w[1]), "=r"(r.w[2]), "=r"(r.w[3])
+               : "l"(p), "l"(policy));
+  return r;
+}
+template <>
+__device__ __forceinline__ Raw<8> ld_stream_hint<8>(const void* p, uint64_t policy) {
+  Raw<8> r;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v2.u32 {%0,%1}, [%2], %3;"
+               : "=r"(r.w[0]), "=r"(r.w[1])
+               : "l"(p), "l"(policy));
+  return r;
+}
+
+template <int VB>
+__device__ __forceinline__ Raw<VB> ld_rw_hint(const void* p, uint64_t policy);
+template <>
+__device__ __forceinline__ Raw<16> ld_rw_hint<16>(const void* p, uint64_t policy) {
+  Raw<16> r;
+  asm volatile("ld.global.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+               : "=r"(r.w[0]), "=r"(r.w[1]), "=r"(r.w[2]), "=r"(r.w[3])
+               : "l"(p), "l"(policy)
+               : "memory");
+  return r;
+}
+template <>
+__device__ __forceinline__ Raw<8> ld_rw_hint<8>(const void* p, uint64_t policy) {
+  Raw<8> r;
+  asm volatile("ld.global.L1::no_allocate.L2::cache_hint.v2.u32 {%0,%1}, [%2], %3;"
+               : "=r"(r.w[0]), "=r"(r.w[1])
+               : "l"(p), "l"(policy)
+               : "memory");
+  return r;
+}
+
+template <int VB>
+__device__ __forceinline__ void st_row_hint(void* p, const Raw<VB>& r, uint64_t policy);
+template <>
+__device__ __forceinline__ void st_row_hint<16>(void* p, const Raw<16>& r, uint64_t policy) {
+  asm volatile("st.global.L2::cache_hint.v4.u32 [%0], {%1,%2,%3,%4}, %5;"
+               :
+               : "l"(p), "r"(r.w[0]), "r"(r.w[1]), "r"(r.w[2]), "r"(r.w[3]), "l"(policy)
+               : "memory");
+}
+template <>
+__device__ __forceinline__ void st_row_hint<8>(void* p, const Raw<8>& r, uint64_t policy) {
+  asm volatile("st.global.L2::cache_hint.v2.u32 [%0], {%1,%2}, %3;"
+               :
+               : "l"(p), "r"(r.w[0]), "r"(r.w[1]), "l"(policy)
+               : "memory");
+}
+
+// Division of a 32-bit unsigned by a run-time constant as multiply + shifts (Granlund & Montgomery,
+// "Division by invariant integers using multiplication", round-up variant); exact for all n.
+struct FastDiv {
+  uint32_t m, s1, s2;
+};
+inline FastDiv make_fastdiv(uint32_t d) {
+  FastDiv f;
+  uint32_t l = 0;
+  while ((1ull << l) < d) ++l;  // ceil(log2 d)
+  f.m = static_cast<uint32_t>(((1ull << 32) * ((1ull << l) - d)) / d + 1);
+  f.s1 = l < 1 ? l : 1;
+  f.s2 = l > 0 ? l - 1 : 0;
+  return f;
+}
+__device__ __forceinline__ uint32_t fastdiv(uint32_t n, const FastDiv& f) {
+  const uint32_t t1 = __umulhi(f.m, n);
+  return (t1 + ((n - t1) >> f.s1)) >> f.s2;
 }
 
 // ---------------------------------------------------------------- element <-> accumulator

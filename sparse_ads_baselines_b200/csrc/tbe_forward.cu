@@ -51,7 +51,7 @@ __global__ void __launch_bounds__(256) tbe_forward_kernel(const FwdArgs a) {
   const int sub = lane & ((1 << lpr_log2) - 1);
   const int slot = lane >> lpr_log2;
   const char* __restrict__ W = static_cast<const char*>(a.weights);
-  const int64_t row_bytes = static_cast<int64_t>(a.D) * sizeof(T);
+  const uint32_t row_bytes = static_cast<uint32_t>(a.D) * static_cast<uint32_t>(sizeof(T));
   const int32_t* __restrict__ offsets = a.offsets;
   const int32_t* __restrict__ indices = a.indices;
   const T* __restrict__ psw = static_cast<const T*>(a.psw);
@@ -78,21 +78,22 @@ __global__ void __launch_bounds__(256) tbe_forward_kernel(const FwdArgs a) {
 
     const int t = static_cast<int>(bag / a.B);
     const int b = static_cast<int>(bag - static_cast<int64_t>(t) * a.B);
-    const int64_t row0 = __ldg(a.table_offsets + t);
+    const uint32_t row0 = static_cast<uint32_t>(__ldg(a.table_offsets + t));
 
     char* outp;
     if (SHARDED) {
       const int dest = b / a.B_local;
       const int bl = b - dest * a.B_local;
       outp = static_cast<char*>(a.out[dest]) +
-             (static_cast<int64_t>(bl) * a.T_total + a.t0 + t) * row_bytes;
+             (static_cast<int64_t>(bl) * a.T_total + a.t0 + t) * static_cast<int64_t>(row_bytes);
     } else {
-      outp = static_cast<char*>(a.out[0]) + (static_cast<int64_t>(b) * a.T + t) * row_bytes;
+      outp = static_cast<char*>(a.out[0]) + (static_cast<int64_t>(b) * a.T + t) * static_cast<int64_t>(row_bytes);
     }
 
     for (int c = 0; c < a.nchunks; ++c) {
       const int v = (c << 5) + sub;
       const bool vact = v < a.nvec;
+      const char* const Wv = W + static_cast<int64_t>(v) * VB;  // this lane's vector of row 0
       acc_t acc[NE];
 #pragma unroll
       for (int k = 0; k < NE; ++k) acc[k] = 0;
@@ -119,7 +120,8 @@ __global__ void __launch_bounds__(256) tbe_forward_kernel(const FwdArgs a) {
             const int idx = __shfl_sync(kFullMask, idx_l, j & 31);
             if (WEIGHTED) w[u] = __shfl_sync(kFullMask, w_l, j & 31);
             if (j < cnt && vact) {
-              r[u] = ld_stream<VB>(W + (row0 + idx) * row_bytes + static_cast<int64_t>(v) * VB);
+              // 32-bit row id times 32-bit row size: one wide multiply-add per address
+              r[u] = ld_stream<VB>(Wv + static_cast<uint64_t>(row0 + static_cast<uint32_t>(idx)) * row_bytes);
             } else {
               r[u] = raw_zero<VB>();
             }
@@ -175,6 +177,8 @@ int launch_fwd(const FwdArgs& a, cudaStream_t stream) {
   int per_sm = 0;
   TBE_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0));
   if (per_sm < 1) per_sm = 1;
+  // knob: blocks per SM of the persistent grid; a value above what fits makes the grid one warp per bag
+  if (tuning(kTuneFwdBlocksPerSM) > 0) per_sm = tuning(kTuneFwdBlocksPerSM);
   const int64_t nbags = static_cast<int64_t>(a.B) * a.T;
   const int wpb = threads / 32;
   int64_t blocks = (nbags + wpb - 1) / wpb;
@@ -221,7 +225,8 @@ int forward_common(const void* weights, const int32_t* table_offsets, const int3
                    const int32_t* offsets, const void* psw, void* const* outs, int world,
                    int64_t T, int64_t B, int64_t D, int64_t T_total, int64_t t0, int dtype,
                    int pooling, bool sharded, void* stream) {
-  TBE_REQUIRE(weights && table_offsets && indices && offsets && outs, "tbe_forward: null pointer argument");
+  // `indices` may be null when every bag is empty: it is only read inside non-empty bag extents
+  TBE_REQUIRE(weights && table_offsets && offsets && outs, "tbe_forward: null pointer argument");
   TBE_REQUIRE(T > 0, "tbe_forward: T must be > 0 (got %lld)", (long long)T);
   TBE_REQUIRE(B > 0, "tbe_forward: B must be > 0 (got %lld)", (long long)B);
   TBE_REQUIRE(D > 0 && D % 4 == 0, "tbe_forward: D must be a positive multiple of 4 (got %lld)", (long long)D);

@@ -113,15 +113,90 @@ def _grad_view(grad_output, B, T, D, weights):
     return grad_output
 
 
-def _backward_workspace(weights, N, total_rows):
+def _workspace_bytes(N, total_rows):
     nbytes = _lib.lib().tbe_backward_workspace_bytes(N, total_rows)
     if nbytes < 0:
         raise _lib.TBEError("tbe_backward_workspace_bytes", nbytes, _lib.last_error())
-    return _workspace(weights.device, nbytes)
+    return nbytes
+
+
+def _backward_workspace(weights, N, total_rows):
+    return _workspace(weights.device, _workspace_bytes(N, total_rows))
+
+
+_max_rows_cache = {}  # (data_ptr, numel, version, total_rows) -> largest table
+
+
+def _max_rows_per_table(table_offsets, total_rows):
+    """Row count of the largest table (lets the sort skip the table bits).  Reads ``table_offsets``
+    back once per distinct tensor -- a host synchronisation on the first call only."""
+    key = (table_offsets.data_ptr(), table_offsets.numel(), table_offsets._version, int(total_rows))
+    v = _max_rows_cache.get(key)
+    if v is None:
+        offs = table_offsets.detach().cpu().tolist() + [int(total_rows)]
+        diffs = [b - a for a, b in zip(offs[:-1], offs[1:])]
+        v = max(diffs) if diffs and min(diffs) >= 0 else 0
+        if len(_max_rows_cache) > 256:
+            _max_rows_cache.clear()
+        _max_rows_cache[key] = v
+    return v
+
+
+_side_streams = {}
+
+
+def _side_stream(device):
+    s = _side_streams.get(device.index)
+    if s is None:
+        s = torch.cuda.Stream(device, priority=-1)  # its short kernels go ahead of the long gathers
+        _side_streams[device.index] = s
+    return s
+
+
+class BackwardPlan:
+    """The index-only half of a backward (sorted lookups), built ahead of time on a side stream."""
+
+    def __init__(self, workspace, event, N, total_rows, max_rows):
+        self.workspace, self.event = workspace, event
+        self.N, self.total_rows, self.max_rows = N, total_rows, max_rows
+
+
+def backward_plan(table_offsets, indices, offsets, total_rows):
+    """Starts sorting the lookups of ``(indices, offsets)`` on a side stream and returns a
+    :class:`BackwardPlan`; pass it as ``plan=`` to a ``backward_*`` call for the same inputs.
+    Nothing here depends on the gradient, so it overlaps with the forward or with an exchange."""
+    _check_cuda("table_offsets", table_offsets, torch.int32)
+    _check_cuda("indices", indices, torch.int32)
+    _check_cuda("offsets", offsets, torch.int32)
+    dev = indices.device
+    T = table_offsets.numel()
+    B = (offsets.numel() - 1) // T
+    N = indices.numel()
+    max_rows = _max_rows_per_table(table_offsets, total_rows)
+    with torch.cuda.device(dev):
+        main, side = torch.cuda.current_stream(dev), _side_stream(dev)
+        ws = torch.empty(_workspace_bytes(N, total_rows), dtype=torch.uint8, device=dev)
+        ws.record_stream(side)
+        side.wait_stream(main)
+        _lib.call("tbe_backward_plan", table_offsets.data_ptr(), indices.data_ptr(), offsets.data_ptr(), T, B, N,
+                  total_rows, max_rows, ws.data_ptr(), ws.numel(), ctypes.c_void_p(side.cuda_stream))
+        event = torch.cuda.Event()
+        event.record(side)
+    return BackwardPlan(ws, event, N, total_rows, max_rows)
+
+
+def _plan_or_workspace(plan, weights, table_offsets, N):
+    """(workspace, max_rows, plan_ready) for a backward call; waits for a prebuilt plan."""
+    total_rows = weights.size(0)
+    if plan is None:
+        return _backward_workspace(weights, N, total_rows), _max_rows_per_table(table_offsets, total_rows), 0
+    _require(plan.N == N and plan.total_rows == total_rows, "the backward plan was built for other inputs")
+    torch.cuda.current_stream(weights.device).wait_event(plan.event)
+    return plan.workspace, plan.max_rows, 1
 
 
 def backward_sgd(grad_output, weights, table_offsets, indices, offsets, learning_rate, L_max, BT_block_size, shmem,
-                 *, pooling_mode="sum"):
+                 *, pooling_mode="sum", plan=None):
     """In-place exact SGD on ``weights`` (reference: batched_embedding_backward_sgd_cuda,
     table_batched_embeddings_cuda.cu:383-435; here repeated rows are summed, not raced)."""
     _check_lookup_args(weights, table_offsets, indices, offsets)
@@ -130,11 +205,11 @@ def backward_sgd(grad_output, weights, table_offsets, indices, offsets, learning
     grad_output = _grad_view(grad_output, B, T, D, weights)
     N = indices.numel()
     with torch.cuda.device(weights.device):
-        ws = _backward_workspace(weights, N, weights.size(0))
+        ws, max_rows, ready = _plan_or_workspace(plan, weights, table_offsets, N)
         _lib.call("tbe_backward_sgd", grad_output.data_ptr(), grad_output.stride(0), grad_output.stride(1),
                   weights.data_ptr(), table_offsets.data_ptr(), indices.data_ptr(), offsets.data_ptr(),
                   T, B, D, N, weights.size(0), _DTYPES[weights.dtype], _POOLING[pooling_mode],
-                  float(learning_rate), ws.data_ptr(), ws.numel(), _stream(weights.device))
+                  float(learning_rate), max_rows, ready, ws.data_ptr(), ws.numel(), _stream(weights.device))
     return None
 
 
@@ -148,7 +223,8 @@ def _philox_inputs(device, increment):
 
 
 def backward_exact_adagrad(grad_output, weights, table_offsets, indices, offsets, indice_weights, optimizer_state,
-                           learning_rate, eps, stochastic_rounding, BT_block_size, *, pooling_mode="sum"):
+                           learning_rate, eps, stochastic_rounding, BT_block_size, *, pooling_mode="sum",
+                           plan=None):
     """In-place exact rowwise Adagrad (reference: batched_embedding_backward_adagrad_exact_cuda,
     table_batched_embeddings_cuda.cu:1589-1705).  Like the reference, per-sample weights are not
     supported by this optimizer."""
@@ -165,12 +241,12 @@ def backward_exact_adagrad(grad_output, weights, table_offsets, indices, offsets
     if stochastic_rounding and weights.dtype == torch.float16:
         seed, offset = _philox_inputs(weights.device, 2 * ((D + 31) // 32))
     with torch.cuda.device(weights.device):
-        ws = _backward_workspace(weights, N, weights.size(0))
+        ws, max_rows, ready = _plan_or_workspace(plan, weights, table_offsets, N)
         _lib.call("tbe_backward_exact_rowwise_adagrad", grad_output.data_ptr(), grad_output.stride(0),
                   grad_output.stride(1), weights.data_ptr(), table_offsets.data_ptr(), indices.data_ptr(),
                   offsets.data_ptr(), optimizer_state.data_ptr(), T, B, D, N, weights.size(0),
                   _DTYPES[weights.dtype], _POOLING[pooling_mode], float(learning_rate), float(eps),
-                  int(bool(stochastic_rounding)), seed, offset, ws.data_ptr(), ws.numel(),
+                  int(bool(stochastic_rounding)), seed, offset, max_rows, ready, ws.data_ptr(), ws.numel(),
                   _stream(weights.device))
     return None
 

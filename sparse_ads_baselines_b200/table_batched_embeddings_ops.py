@@ -5,6 +5,7 @@
 
 Differences, all opt-in or fixes:
   * ``pooling_mode="sum"|"mean"`` keyword (the reference only sums);
+  * ``plan_ahead`` keyword: sort the lookups for the backward on a side stream while the forward runs;
   * SGD sums the gradients of repeated rows before the update (the reference's kernel races on
     them, and its Python branch raises a TypeError at table_batched_embeddings_ops.py:66);
   * tensors must be on a CUDA device: there is no CPU path.
@@ -40,19 +41,23 @@ def _bt_block_hint(embedding_dim):
 def _empty_sparse_grad(weights):
     # The reference hands autograd an empty sparse tensor for the weights slot
     # (table_batched_embeddings_ops.py:111): the real update already happened in place.
-    return torch.sparse_coo_tensor(size=tuple(weights.shape), dtype=weights.dtype, device=weights.device)
+    return torch.empty(tuple(weights.shape), layout=torch.sparse_coo, dtype=weights.dtype, device=weights.device)
 
 
 class LookupFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, weights, table_offsets, indices, offsets, per_sample_weights, optimizer, optimizer_state,
-                learning_rate, eps, stochastic_rounding, pooling_mode="sum"):
+                learning_rate, eps, stochastic_rounding, pooling_mode="sum", plan_ahead=False):
         ctx.optimizer = optimizer
         ctx.learning_rate = learning_rate
         ctx.eps = eps
         ctx.stochastic_rounding = stochastic_rounding
         ctx.pooling_mode = pooling_mode
+        ctx.plan = None
         ctx.save_for_backward(weights, table_offsets, indices, offsets, per_sample_weights, optimizer_state)
+        if (plan_ahead and weights.requires_grad and optimizer != Optimizer.APPROX_ROWWISE_ADAGRAD):
+            # launched before the forward so its kernels are queued first
+            ctx.plan = table_batched_embeddings.backward_plan(table_offsets, indices, offsets, weights.size(0))
         return table_batched_embeddings.forward(
             weights, table_offsets, indices, offsets, per_sample_weights, _L_MAX_HINT,
             _bt_block_hint(weights.shape[1]), False, pooling_mode=pooling_mode)
@@ -66,7 +71,7 @@ class LookupFunction(torch.autograd.Function):
             assert per_sample_weights is None
             table_batched_embeddings.backward_sgd(
                 grad_output, weights, table_offsets, indices, offsets, ctx.learning_rate, _L_MAX_HINT,
-                _bt_block_hint(weights.shape[1]), False, pooling_mode=ctx.pooling_mode)
+                _bt_block_hint(weights.shape[1]), False, pooling_mode=ctx.pooling_mode, plan=ctx.plan)
         elif ctx.optimizer == Optimizer.APPROX_ROWWISE_ADAGRAD:
             assert ctx.pooling_mode == "sum", "approximate rowwise Adagrad supports sum pooling only"
             grad_per_sample_weight = table_batched_embeddings.backward_approx_adagrad(
@@ -75,9 +80,10 @@ class LookupFunction(torch.autograd.Function):
         else:
             table_batched_embeddings.backward_exact_adagrad(
                 grad_output, weights, table_offsets, indices, offsets, per_sample_weights, optimizer_state,
-                ctx.learning_rate, ctx.eps, ctx.stochastic_rounding, 1, pooling_mode=ctx.pooling_mode)
+                ctx.learning_rate, ctx.eps, ctx.stochastic_rounding, 1, pooling_mode=ctx.pooling_mode, plan=ctx.plan)
+        ctx.plan = None
         return (_empty_sparse_grad(weights), None, None, None, grad_per_sample_weight, None, None, None, None,
-                None, None)
+                None, None, None)
 
 
 class TableBatchedEmbeddingBags(nn.Module):
@@ -89,7 +95,7 @@ class TableBatchedEmbeddingBags(nn.Module):
 
     def __init__(self, num_tables, num_embeddings, embedding_dim, optimizer=Optimizer.SGD, learning_rate=0.01,
                  eps=None, stochastic_rounding=False, fp16=False, managed=EmbeddingLocation.DEVICE, *,
-                 pooling_mode="sum"):
+                 pooling_mode="sum", plan_ahead=False):
         super().__init__()
         assert managed in (EmbeddingLocation.DEVICE, EmbeddingLocation.HOST_MAPPED)
         assert pooling_mode in ("sum", "mean")
@@ -114,9 +120,10 @@ class TableBatchedEmbeddingBags(nn.Module):
         self.eps = eps
         self.stochastic_rounding = stochastic_rounding
         self.pooling_mode = pooling_mode
+        self.plan_ahead = plan_ahead
 
     def forward(self, sharded_sparse_features, sharded_offsets, per_sample_weights=None):
         return LookupFunction.apply(
             self.embedding_weights, self.table_offsets, sharded_sparse_features, sharded_offsets,
             per_sample_weights, self.optimizer, self.optimizer_state, self.learning_rate, self.eps,
-            self.stochastic_rounding, self.pooling_mode)
+            self.stochastic_rounding, self.pooling_mode, self.plan_ahead)

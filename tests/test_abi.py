@@ -55,7 +55,7 @@ def test_invalid_arguments_are_rejected_without_a_device(lib):
     assert rc == -1 and b"T must be" in lib.tbe_last_error_string()
     rc = lib.tbe_forward(p, p, p, p, p, p, 1, 1, 4, _lib.TBE_F32, _lib.TBE_POOL_MEAN, None)
     assert rc == -1 and b"per-sample" in lib.tbe_last_error_string()
-    rc = lib.tbe_backward_sgd(p, 4, 4, p, p, p, p, 1, 1, 4, 1, 1, _lib.TBE_F32, 0, 0.1, None, 0, None)
+    rc = lib.tbe_backward_sgd(p, 4, 4, p, p, p, p, 1, 1, 4, 1, 1, _lib.TBE_F32, 0, 0.1, 0, 0, None, 0, None)
     assert rc == -1 and b"workspace" in lib.tbe_last_error_string()
     assert lib.tbe_set_tuning(b"no_such_knob", 1) == -1
     assert lib.tbe_set_tuning(b"fwd_unroll", 0) == 0

@@ -227,7 +227,7 @@ def test_workspace_too_small_is_reported(cuda_device):
     rc = _lib.lib().tbe_backward_sgd(c["grad_d"].data_ptr(), c["T"] * c["D"], c["D"], c["weights_d"].data_ptr(),
                                      c["table_offsets_d"].data_ptr(), c["indices_d"].data_ptr(),
                                      c["offsets_d"].data_ptr(), c["T"], c["B"], c["D"], c["N"], c["T"] * c["E"],
-                                     _lib.TBE_F32, _lib.TBE_POOL_SUM, 0.1, ws.data_ptr(), ws.numel(), None)
+                                     _lib.TBE_F32, _lib.TBE_POOL_SUM, 0.1, 0, 0, ws.data_ptr(), ws.numel(), None)
     assert rc == -2 and b"workspace" in _lib.lib().tbe_last_error_string()
 
 
@@ -252,10 +252,12 @@ def test_full_size_target_step_properties(cuda_device):
     assert bool((rows[1:] >= rows[:-1]).all())
     before = weights.clone()
     tbe.backward_sgd(grad, weights, to, idx, off, w.lr, 200, 2, False)
-    changed = (weights != before).any(dim=1)
     touched = torch.zeros(w.T * w.E, dtype=torch.bool, device=dev)
     touched[rows[starts.long()].long()] = True
-    assert not bool((changed & ~touched).any())
+    for t in range(w.T):  # table by table to bound temporary memory
+        sl = slice(t * w.E, (t + 1) * w.E)
+        changed = (weights[sl] != before[sl]).any(dim=1)
+        assert not bool((changed & ~touched[sl]).any())
     # (3) sampled runs
     starts_c, rows_c, bags_c = starts.cpu().numpy(), rows.cpu().numpy(), bags.cpu().numpy()
     rng = np.random.default_rng(0)
@@ -269,6 +271,10 @@ def test_full_size_target_step_properties(cuda_device):
             g += grad[b, t].float()
         expect = (before[r].float() - w.lr * g).half()
         torch.testing.assert_close(weights[r].float(), expect.float(), rtol=2e-3, atol=1e-5)
-    # (4) round trip
+    # (4) round trip, compared table by table to bound temporary memory
     tbe.backward_sgd(grad, weights, to, idx, off, -w.lr, 200, 2, False)
-    torch.testing.assert_close(weights.float(), before.float(), rtol=0, atol=2.0 ** -16)
+    worst = 0.0
+    for t in range(w.T):
+        sl = slice(t * w.E, (t + 1) * w.E)
+        worst = max(worst, (weights[sl].float() - before[sl].float()).abs().max().item())
+    assert worst <= 2.0 ** -16

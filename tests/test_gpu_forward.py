@@ -10,7 +10,7 @@ from oracle import tbe_oracle as oracle
 from sparse_ads_baselines_b200 import _lib, workloads
 from sparse_ads_baselines_b200 import table_batched_embeddings as tbe
 
-from tbe_testlib import assert_close, make_case, to_device
+from tbe_testlib import assert_close, forward_scale, make_case, to_device
 
 pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
@@ -32,7 +32,7 @@ def test_forward_matches_embeddingbag(cuda_device, D, dtype, pooling, weighted):
     assert out.shape == (c["B"], c["T"], D) and out.dtype == dtype
     ref = oracle.forward(c["weights"], c["table_offsets"], c["indices"], c["offsets"],
                          c["psw"] if weighted else None, pooling, compute_dtype=torch.float32)
-    assert_close(out, ref, dtype)
+    assert_close(out, ref, dtype, scale=forward_scale(c, pooling, weighted))
 
 
 def test_forward_fp64(cuda_device):
@@ -50,7 +50,7 @@ def test_forward_reference_test_shapes(cuda_device, T, B, L):
         c = to_device(make_case(T=T, E=10_000, D=64, B=B, Lmax=L, dtype=dtype, seed=T * 100 + B, fixed_L=L), cuda_device)
         out = _run_forward(c)
         ref = oracle.forward(c["weights"], c["table_offsets"], c["indices"], c["offsets"], compute_dtype=torch.float32)
-        assert_close(out, ref, dtype)
+        assert_close(out, ref, dtype, scale=forward_scale(c))
 
 
 def test_forward_many_bags_covers_persistent_loop(cuda_device):
