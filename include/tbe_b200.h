@@ -166,6 +166,32 @@ TBE_API int tbe_backward_exact_rowwise_adagrad(
     int64_t max_rows_per_table, int plan_ready,
     void* workspace, int64_t workspace_bytes, void* stream);
 
+/* tbe_backward_sgd for callers that cannot provide a workspace because they cannot allocate
+ * device memory: a host that binds this ABI through a bare FFI and has no device allocator of
+ * its own, or a serving process whose HBM is fully budgeted at start-up and which must not
+ * call cudaMalloc (a device-wide synchronisation) while handling a request.  The scratch is
+ * a fixed array inside the library's device image (tbe_noalloc_scratch_bytes() bytes, held
+ * by every GPU that loads the library until the process exits); the call allocates nothing.
+ * Same arguments and results as tbe_backward_sgd without plan_ready / workspace.
+ *  - Limit: N <= TBE_NOALLOC_MAX_LOOKUPS; larger batches are rejected with
+ *    TBE_ERR_WORKSPACE_TOO_SMALL and a message naming the limit.
+ *  - The first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress, with that device current); make that first call before any
+ *    stream capture begins.
+ *  - All calls on a device share the array and it keeps the previous call's contents; the
+ *    words that must start at zero are cleared by every call.  Calls whose GPU work overlaps
+ *    (different streams or threads on one device) race on the array: serialise them.
+ * This entry point has no counterpart in the reference, which allocates its sort scratch with
+ * at::empty on every call (table_batched_embeddings_cuda.cu:1618-1627,1646). */
+#define TBE_NOALLOC_MAX_LOOKUPS 524288
+TBE_API int64_t tbe_noalloc_scratch_bytes(void);
+TBE_API int tbe_backward_sgd_noalloc(const void* grad_output, int64_t stride_b, int64_t stride_t,
+                     void* weights, const int32_t* table_offsets,
+                     const int32_t* indices, const int32_t* offsets,
+                     int64_t T, int64_t B, int64_t D, int64_t N, int64_t total_rows,
+                     int dtype, int pooling, float lr, int64_t max_rows_per_table,
+                     void* stream);
+
 /* Approximate rowwise Adagrad: every lookup is applied on its own, in index order,
  * with its bag's g2 = |grad[b][t]|^2 (times w_l^2 when weighted):
  *   state[r] += g2;  weights[r] -= w_l * lr / (sqrt(state[r]) + eps) * grad[b][t].

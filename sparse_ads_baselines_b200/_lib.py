@@ -33,6 +33,9 @@ SIGNATURES = {
     "tbe_backward_plan": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     "tbe_backward_sgd": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _i32,
                                 _f32, _i64, _i32, _vp, _i64, _vp]),
+    "tbe_noalloc_scratch_bytes": (_i64, []),
+    "tbe_backward_sgd_noalloc": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _i32,
+                                        _f32, _i64, _vp]),
     "tbe_backward_exact_rowwise_adagrad": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64,
                                                   _i64, _i32, _i32, _f32, _f32, _i32, _u64, _u64, _i64, _i32, _vp,
                                                   _i64, _vp]),
