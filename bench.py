@@ -238,7 +238,7 @@ def run_ours(args, rank, world, local_rank):
         del table_of_pos
     gen = torch.Generator(device=device).manual_seed(99 + rank)
     grad = torch.randn(Bl, w.T * world, w.D, device=device, generator=gen).to(tdt)  # upstream gradient, local slice
-    N = batches[0]["N"]
+    N = sum(b["N"] for b in batches) / ROTATE   # mean lookups per step (ragged workloads differ per batch)
     nbags = w.T * w.B
 
     def step(i):
@@ -336,11 +336,12 @@ def run_e2e(args, w, module, batches, grad, backward, tbe, device):
     copied from pinned host memory, the pooled output is copied back, all inside the timed region.
     Copies run on their own streams and are double-buffered against the kernels."""
     depth = 2
-    N = batches[0]["N"]
+    N = sum(b["N"] for b in batches) / len(batches)   # mean lookups per step over the rotating batches
+    n_max = max(b["N"] for b in batches)
     nbags = w.T * w.B
     grad_h = grad.cpu().pin_memory()
     weights, to = module.embedding_weights.data, module.table_offsets
-    d_idx = [torch.empty(N, dtype=torch.int32, device=device) for _ in range(depth)]
+    d_idx = [torch.empty(n_max, dtype=torch.int32, device=device) for _ in range(depth)]
     d_off = [torch.empty(nbags + 1, dtype=torch.int32, device=device) for _ in range(depth)]
     d_grad = [torch.empty_like(grad) for _ in range(depth)]
     d_out = [torch.empty(w.B, w.T, w.D, dtype=grad.dtype, device=device) for _ in range(depth)]
@@ -359,14 +360,15 @@ def run_e2e(args, w, module, batches, grad, backward, tbe, device):
             b = batches[i % ROTATE]
             with torch.cuda.stream(s_in):
                 s_in.wait_event(ev_done[s])  # slot's previous kernels are finished
-                d_idx[s].copy_(b["idx_h"], non_blocking=True)
+                idx_s = d_idx[s][:b["N"]]
+                idx_s.copy_(b["idx_h"], non_blocking=True)
                 d_off[s].copy_(b["off_h"], non_blocking=True)
                 if backward:
                     d_grad[s].copy_(grad_h, non_blocking=True)
                 ev_in[s].record(s_in)
             s_main.wait_event(ev_in[s])
             s_main.wait_event(ev_out[s])  # slot's previous output has left the device
-            tbe.forward(weights, to, d_idx[s], d_off[s], None, 200, 2, False, pooling_mode=w.pooling, out=d_out[s])
+            tbe.forward(weights, to, idx_s, d_off[s], None, 200, 2, False, pooling_mode=w.pooling, out=d_out[s])
             ev_fwd[s].record(s_main)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_fwd[s])
@@ -374,10 +376,10 @@ def run_e2e(args, w, module, batches, grad, backward, tbe, device):
                 ev_out[s].record(s_out)
             if backward:
                 if w.optimizer == "sgd":
-                    tbe.backward_sgd(d_grad[s], weights, to, d_idx[s], d_off[s], w.lr, 200, 2, False,
+                    tbe.backward_sgd(d_grad[s], weights, to, idx_s, d_off[s], w.lr, 200, 2, False,
                                      pooling_mode=w.pooling)
                 else:
-                    tbe.backward_exact_adagrad(d_grad[s], weights, to, d_idx[s], d_off[s], None,
+                    tbe.backward_exact_adagrad(d_grad[s], weights, to, idx_s, d_off[s], None,
                                                module.optimizer_state, w.lr, w.eps, False, 1, pooling_mode=w.pooling)
             ev_done[s].record(s_main)
 
@@ -428,6 +430,8 @@ def main():
             raise SystemExit("--gpus %d needs torchrun with %d ranks (WORLD_SIZE=%d)" % (args.gpus, args.gpus, world))
     if world > 1:
         import torch.distributed as dist
+        # stdout carries the one JSON line only: keep NCCL's version banner off it
+        os.environ["NCCL_DEBUG"] = os.environ.get("TBE_BENCH_NCCL_DEBUG", "WARN")
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:

@@ -209,6 +209,7 @@ TBE_API int tbe_backward_approx_rowwise_adagrad(
     int64_t T, int64_t B, int64_t D, int64_t N, int64_t total_rows,
     int dtype, float lr, float eps,
     int stochastic_rounding, uint64_t sr_seed, uint64_t sr_offset,
+    int64_t max_rows_per_table,
     void* workspace, int64_t workspace_bytes, void* stream);
 
 /* The integer bookkeeping of the backward on its own (what the optimizer kernels

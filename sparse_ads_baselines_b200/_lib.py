@@ -40,8 +40,8 @@ SIGNATURES = {
                                                   _i64, _i32, _i32, _f32, _f32, _i32, _u64, _u64, _i64, _i32, _vp,
                                                   _i64, _vp]),
     "tbe_backward_approx_rowwise_adagrad": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
-                                                   _i64, _i64, _i64, _i32, _f32, _f32, _i32, _u64, _u64, _vp,
-                                                   _i64, _vp]),
+                                                   _i64, _i64, _i64, _i32, _f32, _f32, _i32, _u64, _u64, _i64,
+                                                   _vp, _i64, _vp]),
     "tbe_sort_segments": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
     "tbe_construct_offsets": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp]),
     "tbe_check_inputs": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _vp]),

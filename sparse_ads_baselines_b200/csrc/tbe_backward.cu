@@ -26,30 +26,11 @@
 #include <cub/device/device_select.cuh>
 #include <thrust/iterator/counting_iterator.h>
 
-#include "tbe_common.cuh"
+#include "tbe_plan.cuh"
 
 namespace tbe {
-namespace {
 
-enum Opt { kSGD = 0, kExactAdagrad = 1 };
-
-constexpr int kDefaultLongSegment = 64;
-constexpr int kBwdThreads = 256;
-
-// ------------------------------------------------------------------ workspace
-struct Workspace {
-  uint32_t* keys_in;
-  uint32_t* keys;       // sorted row ids
-  int32_t* vals_in;
-  int32_t* vals;        // bag id of every sorted entry
-  int32_t* seg_starts;  // N + 1 (tbe_sort_segments only)
-  int2* long_list;      // {first sorted position, end position} of queued runs; N/32 + 2 entries
-  int32_t* counters;    // [0] = number of runs (tbe_sort_segments), [1] = queued long runs
-  void* cub_temp;
-  size_t cub_bytes;
-  size_t total;
-};
-
+// ------------------------------------------------------------------ shared host helpers (tbe_plan.cuh)
 // Predicate over positions of the sorted key array: true where a run starts.
 struct RunStart {
   const uint32_t* keys;
@@ -102,11 +83,82 @@ int carve(void* base, int64_t N, int64_t total_rows, Workspace* ws) {
   ws->keys_in = static_cast<uint32_t*>(take(n * 4));
   ws->vals_in = static_cast<int32_t*>(take(n * 4));
   ws->seg_starts = static_cast<int32_t*>(take((n + 1) * 4));
+  ws->entry_bag = static_cast<int32_t*>(take(n * 4));
+  ws->entry_g2 = static_cast<float*>(take(n * 4));
   ws->cub_temp = take(cub_bytes);
   ws->cub_bytes = cub_bytes;
   ws->total = off;
   return TBE_OK;
 }
+
+KeyLayout key_layout(int64_t T, int64_t total_rows, int64_t max_rows_per_table, bool full_order) {
+  KeyLayout k;
+  int ib = 0, tb = 0;
+  if (max_rows_per_table > 0) {
+    ib = 1;
+    while (ib < 32 && (1ll << ib) < max_rows_per_table) ++ib;
+    while ((1ll << tb) < T) ++tb;
+  }
+  if (ib == 0 || ib + tb > 32) {
+    k.idx_bits = 0;
+    k.sort_bits = key_bits(total_rows);
+  } else {
+    k.idx_bits = ib;
+    k.sort_bits = full_order ? (ib + tb > 0 ? ib + tb : 1) : ib;
+  }
+  return k;
+}
+
+int check_sizes(const char* who, int64_t T, int64_t B, int64_t N, int64_t total_rows) {
+  TBE_REQUIRE(T > 0 && B > 0, "%s: T and B must be > 0", who);
+  TBE_REQUIRE(N >= 0 && N < (1ll << 31) - 64, "%s: N out of range", who);
+  TBE_REQUIRE(T * B < (1ll << 31), "%s: B*T out of range", who);
+  TBE_REQUIRE(total_rows > 0 && total_rows < (1ll << 31), "%s: total_rows out of range", who);
+  return TBE_OK;
+}
+
+int prepare_workspace(const char* who, void* workspace, int64_t workspace_bytes, int64_t N, int64_t total_rows,
+                      Workspace* ws) {
+  TBE_REQUIRE(workspace != nullptr, "%s: workspace is null", who);
+  TBE_REQUIRE(reinterpret_cast<uintptr_t>(workspace) % 256 == 0, "%s: workspace must be 256-byte aligned", who);
+  const int rc = carve(workspace, N, total_rows, ws);
+  if (rc != TBE_OK) return rc;
+  if (static_cast<int64_t>(ws->total) > workspace_bytes)
+    return fail(TBE_ERR_WORKSPACE_TOO_SMALL, "%s: workspace has %lld bytes, %lld needed", who,
+                (long long)workspace_bytes, (long long)ws->total);
+  return TBE_OK;
+}
+
+
+int sort_pairs(Workspace& ws, int64_t N, int sort_bits, cudaStream_t stream) {
+  size_t bytes = ws.cub_bytes;
+  {
+    KernelTimer timer("cub_radix_sort_pairs", stream);
+    TBE_CUDA_TRY(cub::DeviceRadixSort::SortPairs(ws.cub_temp, bytes, static_cast<const uint32_t*>(ws.keys_in),
+                                                ws.keys, static_cast<const int32_t*>(ws.vals_in), ws.vals, N, 0,
+                                                sort_bits, stream));
+  }
+  count_library_launch();
+  return TBE_OK;
+}
+
+int select_run_starts(Workspace& ws, int64_t N, cudaStream_t stream) {
+  size_t bytes = ws.cub_bytes;
+  thrust::counting_iterator<int32_t> it(0);
+  {
+    KernelTimer timer("cub_select_run_starts", stream);
+    TBE_CUDA_TRY(cub::DeviceSelect::If(ws.cub_temp, bytes, it, ws.seg_starts, ws.counters, N, RunStart{ws.keys}, stream));
+  }
+  count_library_launch();
+  return TBE_OK;
+}
+
+namespace {
+
+enum Opt { kSGD = 0, kExactAdagrad = 1 };
+
+constexpr int kDefaultLongSegment = 64;
+constexpr int kBwdThreads = 256;
 
 // ------------------------------------------------------------------ step 1: linearize
 // One warp per bag, lanes stride over the bag's index positions.
@@ -130,32 +182,6 @@ __global__ void __launch_bounds__(256) linearize_kernel(const int32_t* __restric
   }
 }
 
-// How the sort keys are formed.  Lookups arrive grouped by table, and a stable sort on the index
-// bits alone already brings equal (table, index) pairs together (ordered by index, then table), so
-// with composite keys only idx_bits need sorting instead of log2(total_rows).
-struct KeyLayout {
-  int idx_bits;   // 0: keys are linear row ids
-  int sort_bits;  // bits the radix sort looks at
-};
-
-KeyLayout key_layout(int64_t T, int64_t total_rows, int64_t max_rows_per_table, bool full_order) {
-  KeyLayout k;
-  int ib = 0, tb = 0;
-  if (max_rows_per_table > 0) {
-    ib = 1;
-    while (ib < 32 && (1ll << ib) < max_rows_per_table) ++ib;
-    while ((1ll << tb) < T) ++tb;
-  }
-  if (ib == 0 || ib + tb > 32) {
-    k.idx_bits = 0;
-    k.sort_bits = key_bits(total_rows);
-  } else {
-    k.idx_bits = ib;
-    k.sort_bits = full_order ? (ib + tb > 0 ? ib + tb : 1) : ib;
-  }
-  return k;
-}
-
 // Steps 1-2.  Leaves the sorted pairs in ws.keys / ws.vals.
 int build_plan(const int32_t* table_offsets, const int32_t* indices, const int32_t* offsets, int64_t T,
                int64_t B, int64_t N, KeyLayout layout, Workspace& ws, cudaStream_t stream) {
@@ -170,15 +196,7 @@ int build_plan(const int32_t* table_offsets, const int32_t* indices, const int32
         table_offsets, indices, offsets, static_cast<int32_t>(B), nbags, layout.idx_bits, ws.keys_in, ws.vals_in);
   }
   TBE_CHECK_LAUNCH("linearize_kernel");
-  size_t bytes = ws.cub_bytes;
-  {
-    KernelTimer timer("cub_radix_sort_pairs", stream);
-    TBE_CUDA_TRY(cub::DeviceRadixSort::SortPairs(ws.cub_temp, bytes, static_cast<const uint32_t*>(ws.keys_in),
-                                                ws.keys, static_cast<const int32_t*>(ws.vals_in), ws.vals,
-                                                static_cast<int64_t>(N), 0, layout.sort_bits, stream));
-  }
-  count_library_launch();
-  return TBE_OK;
+  return sort_pairs(ws, N, layout.sort_bits, stream);
 }
 
 // ------------------------------------------------------------------ steps 3/4: run kernels
@@ -283,12 +301,6 @@ __device__ __forceinline__ void apply_update(char* wp, const Raw<VB>& wraw, cons
 #pragma unroll
   for (int k = 0; k < NE; ++k) w[k] -= G[k] * mult;
   st_row_hint<VB>(wp, pack_out<T, VB, SR>(w, rng), streaming);
-}
-
-// Row of `weights` a sort key stands for.
-__device__ __forceinline__ uint32_t key_to_row(const BwdArgs& a, uint32_t key) {
-  if (a.idx_bits == 0) return key;
-  return static_cast<uint32_t>(__ldg(a.table_offsets + (key >> a.idx_bits))) + (key & ((1u << a.idx_bits) - 1u));
 }
 
 // First position >= lo in the sorted keys whose key differs from `row` (keys[lo-1] == row).
@@ -410,7 +422,7 @@ __global__ void __launch_bounds__(kBwdThreads) run_kernel(const BwdArgs a) {
     // invalid lanes describe entry 0 of the tile so that anything read through them is valid memory
     const uint32_t key0 = __shfl_sync(kFullMask, cur.key, 0);
     const int32_t val0 = __shfl_sync(kFullMask, cur.val, 0);
-    const uint32_t my_row = key_to_row(a, valid ? cur.key : key0);
+    const uint32_t my_row = key_to_row(a.table_offsets, a.idx_bits, valid ? cur.key : key0);
     acc_t my_scale = 1;
     const uint32_t my_goff = grad_units(static_cast<uint32_t>(valid ? cur.val : val0), &my_scale);
     unsigned mine = smask & own_lanes;
@@ -625,7 +637,7 @@ __global__ void __launch_bounds__(kBwdThreads) run_kernel_wide(const BwdArgs a) 
         }
       }
       const int maxlen = __reduce_max_sync(kFullMask, len);
-      const uint32_t wrow_id = has ? key_to_row(a, row) : 0u;
+      const uint32_t wrow_id = has ? key_to_row(a.table_offsets, a.idx_bits, row) : 0u;
       char* wrow = static_cast<char*>(a.weights) + static_cast<int64_t>(wrow_id) * row_bytes;
 
       // sums vector v of the run's gradient rows into acc (tile part with shuffled bag ids, then the tail)
@@ -709,7 +721,7 @@ __global__ void __launch_bounds__(kBwdThreads) long_run_kernel(const BwdArgs a) 
   for (int li = blockIdx.x; li < nlong; li += gridDim.x) {
     const int2 run = a.long_list[li];
     const int s = run.x, len = run.y - run.x;
-    const uint32_t row = key_to_row(a, __ldg(a.keys + s));
+    const uint32_t row = key_to_row(a.table_offsets, a.idx_bits, __ldg(a.keys + s));
     char* wrow = static_cast<char*>(a.weights) + static_cast<int64_t>(row) * row_bytes;
 
     // Folds the groups' partial sums for chunk c in group order; every thread of warp 0 ends with the
@@ -867,26 +879,6 @@ int dispatch_bwd(const BwdArgs& a, int dtype, int vb, bool mean, bool sr, cudaSt
   return fail(TBE_ERR_INVALID_ARGUMENT, "unknown dtype %d", dtype);
 }
 
-int check_sizes(const char* who, int64_t T, int64_t B, int64_t N, int64_t total_rows) {
-  TBE_REQUIRE(T > 0 && B > 0, "%s: T and B must be > 0", who);
-  TBE_REQUIRE(N >= 0 && N < (1ll << 31) - 64, "%s: N out of range", who);
-  TBE_REQUIRE(T * B < (1ll << 31), "%s: B*T out of range", who);
-  TBE_REQUIRE(total_rows > 0 && total_rows < (1ll << 31), "%s: total_rows out of range", who);
-  return TBE_OK;
-}
-
-int prepare_workspace(const char* who, void* workspace, int64_t workspace_bytes, int64_t N, int64_t total_rows,
-                      Workspace* ws) {
-  TBE_REQUIRE(workspace != nullptr, "%s: workspace is null", who);
-  TBE_REQUIRE(reinterpret_cast<uintptr_t>(workspace) % 256 == 0, "%s: workspace must be 256-byte aligned", who);
-  const int rc = carve(workspace, N, total_rows, ws);
-  if (rc != TBE_OK) return rc;
-  if (static_cast<int64_t>(ws->total) > workspace_bytes)
-    return fail(TBE_ERR_WORKSPACE_TOO_SMALL, "%s: workspace has %lld bytes, %lld needed", who,
-                (long long)workspace_bytes, (long long)ws->total);
-  return TBE_OK;
-}
-
 int exact_backward(int opt, const void* grad, int64_t stride_b, int64_t stride_t, void* weights,
                    const int32_t* table_offsets, const int32_t* indices, const int32_t* offsets, float* state,
                    int64_t T, int64_t B, int64_t D, int64_t N, int64_t total_rows, int dtype, int pooling,
@@ -1027,14 +1019,8 @@ extern "C" int tbe_sort_segments(const int32_t* table_offsets, const int32_t* in
   }
   rc = build_plan(table_offsets, indices, offsets, T, B, N, key_layout(T, total_rows, 0, true), ws, stream);
   if (rc != TBE_OK) return rc;
-  size_t bytes = ws.cub_bytes;
-  thrust::counting_iterator<int32_t> it(0);
-  {
-    KernelTimer timer("cub_select_run_starts", stream);
-    TBE_CUDA_TRY(cub::DeviceSelect::If(ws.cub_temp, bytes, it, ws.seg_starts, ws.counters, static_cast<int64_t>(N),
-                                       RunStart{ws.keys}, stream));
-  }
-  count_library_launch();
+  rc = select_run_starts(ws, N, stream);
+  if (rc != TBE_OK) return rc;
   TBE_CUDA_TRY(cudaMemcpyAsync(sorted_rows, ws.keys, N * 4, cudaMemcpyDeviceToDevice, stream));
   TBE_CUDA_TRY(cudaMemcpyAsync(sorted_bags, ws.vals, N * 4, cudaMemcpyDeviceToDevice, stream));
   TBE_CUDA_TRY(cudaMemcpyAsync(segment_starts, ws.seg_starts, N * 4, cudaMemcpyDeviceToDevice, stream));

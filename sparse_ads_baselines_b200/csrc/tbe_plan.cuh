@@ -1,0 +1,52 @@
+// Host-side pieces shared by the backward kernels: the layout of the caller's workspace, the sort
+// key layout, and thin wrappers around the two CUB calls (defined once, in tbe_backward.cu, so that
+// CUB is instantiated in a single translation unit).
+#pragma once
+
+#include "tbe_common.cuh"
+
+namespace tbe {
+
+struct Workspace {
+  uint32_t* keys_in;
+  uint32_t* keys;       // sorted keys
+  int32_t* vals_in;
+  int32_t* vals;        // value of every sorted entry: bag id (exact/SGD) or index position (approx)
+  int32_t* seg_starts;  // N + 1: first sorted position of every run (approx backward, tbe_sort_segments)
+  int2* long_list;      // {first sorted position, end position} of queued runs; N/32 + 2 entries
+  int32_t* entry_bag;   // N: bag id of every index position (approx backward)
+  float* entry_g2;      // N: squared gradient norm applied by every index position (approx backward)
+  int32_t* counters;    // [0] = number of runs, [1] = queued long runs
+  void* cub_temp;
+  size_t cub_bytes;
+  size_t total;
+};
+
+// How the sort keys are formed.  Lookups arrive grouped by table, and a stable sort on the index
+// bits alone already brings equal (table, index) pairs together (ordered by index, then table), so
+// with composite keys only idx_bits need sorting instead of log2(total_rows).
+struct KeyLayout {
+  int idx_bits;   // 0: keys are linear row ids; > 0: keys are (table << idx_bits | index)
+  int sort_bits;  // bits the radix sort looks at
+};
+
+KeyLayout key_layout(int64_t T, int64_t total_rows, int64_t max_rows_per_table, bool full_order);
+
+// Carves the workspace; with base == nullptr only sizes are computed.
+int carve(void* base, int64_t N, int64_t total_rows, Workspace* ws);
+int check_sizes(const char* who, int64_t T, int64_t B, int64_t N, int64_t total_rows);
+int prepare_workspace(const char* who, void* workspace, int64_t workspace_bytes, int64_t N, int64_t total_rows,
+                      Workspace* ws);
+
+// keys_in/vals_in -> keys/vals, stable, on the low sort_bits bits.
+int sort_pairs(Workspace& ws, int64_t N, int sort_bits, cudaStream_t stream);
+// seg_starts[0..U) = first position of every run of equal sorted keys, counters[0] = U.
+int select_run_starts(Workspace& ws, int64_t N, cudaStream_t stream);
+
+// Row of `weights` a sort key stands for.
+__device__ __forceinline__ uint32_t key_to_row(const int32_t* __restrict__ table_offsets, int idx_bits, uint32_t key) {
+  if (idx_bits == 0) return key;
+  return static_cast<uint32_t>(__ldg(table_offsets + (key >> idx_bits))) + (key & ((1u << idx_bits) - 1u));
+}
+
+}  // namespace tbe

@@ -232,9 +232,12 @@ def backward_exact_adagrad(grad_output, weights, table_offsets, indices, offsets
     T, B, D = _geometry(weights, table_offsets, offsets)
     _require(BT_block_size > 0, "BT_block_size must be > 0")
     _require(indice_weights is None, "exact rowwise Adagrad does not support per-sample weights")
-    _check_cuda("optimizer_state", optimizer_state, torch.float32)
+    _check_cuda("optimizer_state", optimizer_state)
     _require(optimizer_state.numel() == weights.size(0) and optimizer_state.is_contiguous(),
-             "optimizer_state must be a contiguous float32 [total_rows] tensor")
+             "optimizer_state must be a contiguous [total_rows] tensor")
+    state_arg = optimizer_state
+    if optimizer_state.dtype != torch.float32:  # see backward_approx_adagrad
+        optimizer_state = state_arg.float()
     grad_output = _grad_view(grad_output, B, T, D, weights)
     N = indices.numel()
     seed, offset = (0, 0)
@@ -248,6 +251,8 @@ def backward_exact_adagrad(grad_output, weights, table_offsets, indices, offsets
                   _DTYPES[weights.dtype], _POOLING[pooling_mode], float(learning_rate), float(eps),
                   int(bool(stochastic_rounding)), seed, offset, max_rows, ready, ws.data_ptr(), ws.numel(),
                   _stream(weights.device))
+        if optimizer_state is not state_arg:
+            state_arg.copy_(optimizer_state)
     return None
 
 
@@ -259,9 +264,14 @@ def backward_approx_adagrad(grad_output, weights, table_offsets, indices, offset
     _check_lookup_args(weights, table_offsets, indices, offsets)
     T, B, D = _geometry(weights, table_offsets, offsets)
     _require(BT_block_size > 0, "BT_block_size must be > 0")
-    _check_cuda("optimizer_state", optimizer_state, torch.float32)
+    _check_cuda("optimizer_state", optimizer_state)
     _require(optimizer_state.numel() == weights.size(0) and optimizer_state.is_contiguous(),
-             "optimizer_state must be a contiguous float32 [total_rows] tensor")
+             "optimizer_state must be a contiguous [total_rows] tensor")
+    # the kernels keep the rowwise state in fp32; a module cast with .double() (gradient checks) has a
+    # float64 buffer, which is converted around the call
+    state_arg = optimizer_state
+    if optimizer_state.dtype != torch.float32:
+        optimizer_state = state_arg.float()
     grad_output = _grad_view(grad_output, B, T, D, weights)
     N = indices.numel()
     psw = grad_psw = None
@@ -280,8 +290,11 @@ def backward_approx_adagrad(grad_output, weights, table_offsets, indices, offset
                   offsets.data_ptr(), psw.data_ptr() if psw is not None else None,
                   grad_psw.data_ptr() if grad_psw is not None else None, optimizer_state.data_ptr(),
                   T, B, D, N, weights.size(0), _DTYPES[weights.dtype], float(learning_rate), float(eps),
-                  int(bool(stochastic_rounding)), seed, offset, ws.data_ptr(), ws.numel(),
+                  int(bool(stochastic_rounding)), seed, offset,
+                  _max_rows_per_table(table_offsets, weights.size(0)), ws.data_ptr(), ws.numel(),
                   _stream(weights.device))
+        if optimizer_state is not state_arg:
+            state_arg.copy_(optimizer_state)
     return grad_psw
 
 

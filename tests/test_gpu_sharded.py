@@ -1,0 +1,96 @@
+"""Table-sharded TBE on 2 (or 4) GPUs: the fused peer-store exchange and the NCCL exchange against
+the single-process oracle.  Needs at least two GPUs; child processes, one per GPU."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from oracle import tbe_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_case(rank, Tl, E, D, B, Lmax, dtype):
+    rng = np.random.default_rng(1000 + rank)
+    lengths = rng.integers(0, Lmax + 1, size=(Tl, B))
+    offsets = oracle.offsets_from_lengths(lengths)
+    indices = rng.integers(0, E, size=int(offsets[-1])).astype(np.int32)
+    weights = torch.from_numpy(rng.uniform(-1, 1, size=(Tl * E, D)).astype(np.float32)).to(dtype)
+    return indices, offsets, weights
+
+
+def _worker(rank, world, port, exchange, dtype_name, failures):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from sparse_ads_baselines_b200 import table_batched_embeddings_ops as ops
+        from sparse_ads_baselines_b200.sharded import TableShardedEmbeddingBags
+        dtype = torch.float16 if dtype_name == "fp16" else torch.float32
+        Tl, E, D, B, Lmax, lr = 3, 50, 64, 8 * world, 5, 0.05
+        cases = [_rank_case(r, Tl, E, D, B, Lmax, dtype) for r in range(world)]
+        to = [t * E for t in range(Tl)]
+        # oracle: every rank's local pooled rows, exchanged
+        local = [oracle.forward(w, to, i, o, compute_dtype=torch.float32) for (i, o, w) in cases]
+        expect_out = oracle.all_to_all_pooled(local)[rank]
+        g = torch.Generator().manual_seed(7)
+        grads = [torch.randn(B // world, Tl * world, D, generator=g).to(dtype) for _ in range(world)]
+        grad_in = oracle.all_to_all_pooled_backward(grads)[rank]
+        idx, off, w0 = cases[rank]
+        expect_w = oracle.sgd_step(w0, to, idx, off, grad_in, lr, compute_dtype=torch.float32)
+
+        m = TableShardedEmbeddingBags(Tl, E, D, B, optimizer=ops.Optimizer.SGD, learning_rate=lr,
+                                      fp16=(dtype == torch.float16), exchange=exchange).to(dev)
+        m.tbe.embedding_weights.data.copy_(w0.to(dev))
+        idx_d, off_d = torch.from_numpy(idx).to(dev), torch.from_numpy(off).to(dev)
+        tol = dict(rtol=1e-2, atol=1e-2) if dtype == torch.float16 else dict(rtol=1e-5, atol=1e-5)
+        for step in range(2):  # twice: buffers are reused across iterations
+            m.tbe.embedding_weights.data.copy_(w0.to(dev))
+            out = m(idx_d, off_d)
+            assert tuple(out.shape) == (B // world, Tl * world, D)
+            torch.testing.assert_close(out.detach().float().cpu(), expect_out.float(), **tol)
+            out.backward(grads[rank].to(dev))
+            torch.cuda.synchronize()
+            torch.testing.assert_close(m.tbe.embedding_weights.detach().float().cpu(), expect_w.float(), **tol)
+    except Exception as e:
+        failures.put("rank %d: %r" % (rank, e))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("exchange", ["nccl", "fused"])
+@pytest.mark.parametrize("dtype_name", ["fp32", "fp16"])
+def test_sharded_forward_backward(exchange, dtype_name):
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    ctx = mp.get_context("spawn")
+    failures = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, exchange, dtype_name, failures)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+    hung = [p for p in procs if p.is_alive()]
+    for p in hung:
+        p.kill()
+    msgs = []
+    while not failures.empty():
+        msgs.append(failures.get())
+    assert not hung, "a rank did not finish: %s" % msgs
+    assert not msgs, msgs
+    assert all(p.exitcode == 0 for p in procs)
