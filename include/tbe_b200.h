@@ -255,6 +255,56 @@ TBE_API int tbe_free_managed(void* ptr);
 TBE_API int tbe_alloc_host_mapped(void** host_ptr, void** device_ptr, int64_t bytes);
 TBE_API int tbe_free_host_mapped(void* host_ptr);
 
+/* ---- LXU cache: set-associative HBM cache in front of a host-resident table ---- */
+
+/* The reference has no cache: its only mechanism for tables larger than HBM is
+ * host-mapped memory with every lookup crossing the host link
+ * (table_batched_embeddings_ops.py:159-167, table_batched_embeddings_cuda.cu:797-812).
+ * These entry points have no counterpart there.
+ *
+ * State owned by the caller, all in device memory unless noted:
+ *   cache_rows [num_sets*ways][D]  cached rows (table dtype)
+ *   tags       int32 [num_sets*ways]  row id held by each way, -1 = empty (initialise to -1)
+ *   last_use   int32 [num_sets*ways]  step of the last lookup (initialise to 0)
+ *   use_count  int32 [num_sets*ways]  steps that looked the row up since it was inserted (0)
+ *   dirty      uint8 [num_sets*ways]  row differs from the host copy (0)
+ *   host_rows  [total_rows][D]  the table, in device-mapped pinned host memory
+ * Placement: row r lives in set r % num_sets.  Per step (now = 1, 2, ...): every distinct
+ * row of the batch is looked up first (a hit refreshes last_use and use_count); then the
+ * misses of a set claim, in ascending row order, a way that was not used in this step --
+ * an empty one first, else the one with the smallest last_use (policy 0, LRU) or the
+ * smallest use_count (policy 1, LFU), ties to the lowest way; a dirty victim is written
+ * back to host_rows and the new row is fetched.  A row whose set has no free way stays
+ * uncached for this step and is served from host_rows.
+ *
+ * tbe_cache_prefetch does all of that for one batch and writes locations[p] (int32 [N]):
+ * the cache slot (set*ways + way) holding the row of lookup p, or -1 = read host_rows.
+ * stats (int32 [5], device): {distinct rows, rows fetched, lookups whose row was already
+ * cached, distinct rows already cached, distinct rows left uncached}.  The workspace keeps
+ * the sorted lookups for tbe_cache_backward_sgd of the same batch. */
+TBE_API int64_t tbe_cache_workspace_bytes(int64_t N, int64_t total_rows);
+TBE_API int tbe_cache_prefetch(void* cache_rows, int32_t* tags, int32_t* last_use, int32_t* use_count,
+                               uint8_t* dirty, void* host_rows, const int32_t* table_offsets,
+                               const int32_t* indices, const int32_t* offsets, int32_t* locations,
+                               int32_t* stats, int64_t T, int64_t B, int64_t D, int64_t N,
+                               int64_t total_rows, int64_t num_sets, int ways, int dtype, int policy,
+                               int now, void* workspace, int64_t workspace_bytes, void* stream);
+/* Pooled forward reading every row through `locations` (sum / mean, fp16 / fp32). */
+TBE_API int tbe_cache_forward(const void* cache_rows, const void* host_rows,
+                              const int32_t* table_offsets, const int32_t* indices,
+                              const int32_t* offsets, const int32_t* locations, void* output,
+                              int64_t T, int64_t B, int64_t D, int dtype, int pooling, void* stream);
+/* Exact SGD on the rows of the batch tbe_cache_prefetch last prepared in `workspace`:
+ * cached rows are updated in HBM and marked dirty, uncached rows are updated in host_rows. */
+TBE_API int tbe_cache_backward_sgd(const void* grad_output, int64_t stride_b, int64_t stride_t,
+                                   void* cache_rows, void* host_rows, uint8_t* dirty,
+                                   const int32_t* offsets, int64_t T, int64_t B, int64_t D, int64_t N,
+                                   int64_t total_rows, int64_t num_sets, int dtype, int pooling, float lr,
+                                   void* workspace, int64_t workspace_bytes, void* stream);
+/* Writes every dirty cached row back to host_rows. */
+TBE_API int tbe_cache_flush(void* cache_rows, void* host_rows, const int32_t* tags, uint8_t* dirty,
+                            int64_t num_slots, int64_t D, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

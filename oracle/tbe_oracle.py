@@ -273,3 +273,78 @@ class PerTableEmbeddingBags:
                 out.backward(g)
                 bag.weight.data.add_(bag.weight.grad, alpha=-lr)
         return outs
+
+
+# ------------------------------------------------------------------ LXU cache model
+class LXUCacheModel:
+    """CPU model of the set-associative row cache (no counterpart in the reference: parity unpinned
+    by it; this model IS the specification the CUDA cache is compared with, slot by slot).
+
+    Row r lives in set ``r % num_sets``.  Per step, with ``now`` = 1, 2, ...: every distinct row of
+    the batch is looked up first -- a hit sets ``last_use = now`` and adds one to ``use_count`` --
+    then the misses of each set, in ascending row order, claim a way with ``last_use < now`` (or an
+    empty one): empty ways first, then the smallest ``last_use`` (LRU) or the smallest
+    ``use_count`` (LFU), ties to the lowest way.  A claimed way gets ``last_use = now``,
+    ``use_count = 1``.  A miss with no claimable way stays uncached for the step (location -1)."""
+
+    def __init__(self, num_sets, ways, policy="lru"):
+        self.num_sets, self.ways, self.policy = num_sets, ways, policy
+        self.tags = np.full(num_sets * ways, -1, dtype=np.int32)
+        self.last_use = np.zeros(num_sets * ways, dtype=np.int32)
+        self.use_count = np.zeros(num_sets * ways, dtype=np.int32)
+        self.now = 0
+
+    def step(self, table_offsets, indices, offsets):
+        """Returns (locations int32 [N], stats dict) for one batch and updates the model."""
+        self.now += 1
+        indices = np.asarray(indices, dtype=np.int64)
+        offsets = np.asarray(offsets, dtype=np.int64)
+        T = len(table_offsets)
+        B = (len(offsets) - 1) // T
+        bag_of_pos = np.repeat(np.arange(T * B, dtype=np.int64), np.diff(offsets))
+        rows = np.asarray([int(x) for x in table_offsets], dtype=np.int64)[bag_of_pos // B] + indices
+        uniq, counts = np.unique(rows, return_counts=True)
+        where = {}
+        hit_lookups = hit_rows = 0
+        by_set = {}
+        for r, c in zip(uniq.tolist(), counts.tolist()):
+            by_set.setdefault(r % self.num_sets, []).append((r, c))
+        fetched = uncached = 0
+        for s, members in by_set.items():
+            base = s * self.ways
+            misses = []
+            for r, c in members:  # hits first
+                hit = [w for w in range(self.ways) if self.tags[base + w] == r]
+                if hit:
+                    w = hit[0]
+                    self.last_use[base + w] = self.now
+                    self.use_count[base + w] += 1
+                    where[r] = base + w
+                    hit_lookups += c
+                    hit_rows += 1
+                else:
+                    misses.append(r)
+            for r in sorted(misses):
+                best = None
+                for w in range(self.ways):
+                    slot = base + w
+                    if self.tags[slot] >= 0 and self.last_use[slot] >= self.now:
+                        continue
+                    prio = 0 if self.tags[slot] < 0 else int(self.last_use[slot] if self.policy == "lru"
+                                                             else self.use_count[slot]) + 1
+                    if best is None or (prio, w) < best:
+                        best = (prio, w)
+                if best is None:
+                    where[r] = -1
+                    uncached += 1
+                    continue
+                slot = base + best[1]
+                self.tags[slot] = r
+                self.last_use[slot] = self.now
+                self.use_count[slot] = 1
+                where[r] = slot
+                fetched += 1
+        loc = np.asarray([where[r] for r in rows.tolist()], dtype=np.int32)
+        stats = {"lookups": len(rows), "rows": len(uniq), "fetched": fetched, "hit_lookups": hit_lookups,
+                 "hit_rows": hit_rows, "uncached": uncached}
+        return loc, stats

@@ -1,0 +1,665 @@
+// LXU cache: a set-associative cache in HBM in front of a host-resident embedding table (sm_100a).
+//
+// The table lives in pinned, device-mapped host memory (every uncached access crosses the host
+// link); `ways * num_sets` rows of it are kept in HBM.  Once per step, before the lookup:
+//
+//   1. cache_keys_kernel  : key[p] = (row % num_sets) * Q + row / num_sets for every lookup p
+//                           (Q = ceil(total_rows / num_sets); a bijection of the row id that sorts
+//                           by set first, then by row), value[p] = p
+//   2. radix sort + run starts (CUB): equal rows adjacent, the rows of one set adjacent and
+//                           ascending
+//   3. cache_update_kernel: one lane group per set touched this step, one lane per way holding that
+//                           way's tag / last-use / use-count in registers.  First every distinct
+//                           row of the set is looked up (a hit refreshes the way), then the misses
+//                           claim, in ascending row order, the least-recently (LRU) or
+//                           least-frequently (LFU) used way not used in this step; ties go to the
+//                           lowest way.  If no way is free the row stays uncached for this step.
+//   4. cache_fill_kernel  : one warp per claimed way: the dirty victim row is written back to the
+//                           host table, the new row is fetched into HBM
+//   5. cache_locate_kernel: every lookup position learns where its row is: a cache slot or the host
+//
+// The cached forward / backward read rows through that per-position location.  The policy is
+// deterministic, so tags, counters and hit counts can be compared exactly with a CPU model.
+#include "tbe_plan.cuh"
+
+namespace tbe {
+namespace {
+
+enum Policy { kLRU = 0, kLFU = 1 };
+
+struct CacheArgs {
+  // cache state
+  void* cache_rows;
+  int32_t* tags;       // [num_sets * ways] row id or -1
+  int32_t* last_use;   // [num_sets * ways] step of the last lookup
+  int32_t* use_count;  // [num_sets * ways] lookups steps since insertion (LFU)
+  uint8_t* dirty;      // [num_sets * ways]
+  void* host_rows;     // device-mapped host table
+  // lookups
+  const int32_t* table_offsets;
+  const int32_t* indices;
+  const int32_t* offsets;
+  // plan scratch
+  uint32_t* keys_in;
+  int32_t* vals_in;
+  const uint32_t* keys;
+  const int32_t* vals;
+  const int32_t* seg_starts;
+  int32_t* counters;    // [0] runs, [2] claims, [3] hit lookups, [4] hit rows, [5] uncached rows
+  int32_t* entry_bag;   // bag of every position
+  int32_t* run_loc;     // per run: slot or -1
+  int4* claims;         // {slot, old_tag, new_row, 0}
+  int32_t* loc;         // per position: slot or -1 (output)
+  int32_t* loc_sorted;  // per sorted entry: slot or -1
+  int32_t B, T, D, N;
+  int32_t num_sets, ways_log2, Q;
+  FastDiv div_sets, div_q;
+  int32_t now, policy;
+  int32_t nvec;
+};
+
+__device__ __forceinline__ uint32_t cache_key(const CacheArgs& a, uint32_t row) {
+  const uint32_t q = fastdiv(row, a.div_sets);
+  const uint32_t set = row - q * static_cast<uint32_t>(a.num_sets);
+  return set * static_cast<uint32_t>(a.Q) + q;
+}
+__device__ __forceinline__ void cache_unkey(const CacheArgs& a, uint32_t key, uint32_t* set, uint32_t* row) {
+  const uint32_t s = fastdiv(key, a.div_q);
+  const uint32_t q = key - s * static_cast<uint32_t>(a.Q);
+  *set = s;
+  *row = q * static_cast<uint32_t>(a.num_sets) + s;
+}
+
+__global__ void __launch_bounds__(256) cache_keys_kernel(const CacheArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int64_t nbags = static_cast<int64_t>(a.B) * a.T;
+  const int64_t wstride = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  for (int64_t bag = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); bag < nbags;
+       bag += wstride) {
+    const int t = static_cast<int>(bag / a.B);
+    const uint32_t row0 = static_cast<uint32_t>(__ldg(a.table_offsets + t));
+    const int s = __ldg(a.offsets + bag), e = __ldg(a.offsets + bag + 1);
+    for (int p = s + lane; p < e; p += 32) {
+      a.keys_in[p] = cache_key(a, row0 + static_cast<uint32_t>(__ldg(a.indices + p)));
+      a.vals_in[p] = p;
+      a.entry_bag[p] = static_cast<int32_t>(bag);
+    }
+  }
+}
+
+// One group of `ways` lanes per run; the group whose run is the first of its set walks all runs of
+// the set.
+__global__ void __launch_bounds__(256) cache_update_kernel(const CacheArgs a) {
+  const int ways = 1 << a.ways_log2;
+  const int lane = threadIdx.x & 31;
+  const int way = lane & (ways - 1);
+  const int gpw = 32 >> a.ways_log2;
+  const unsigned gmask = (ways == 32) ? kFullMask : (((1u << ways) - 1u) << (lane & ~(ways - 1)));
+  const int U = a.counters[0];
+  const int64_t gstride = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5) * gpw;
+  for (int64_t u0 = (static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * gpw +
+                    (lane >> a.ways_log2);
+       u0 - (lane >> a.ways_log2) < U; u0 += gstride) {
+    // (the loop bound is warp-uniform; groups past the end idle)
+    bool leader = false;
+    uint32_t set = 0, row = 0;
+    if (u0 < U) {
+      cache_unkey(a, __ldg(a.keys + __ldg(a.seg_starts + u0)), &set, &row);
+      leader = true;
+      if (u0 > 0) {
+        uint32_t pset, prow;
+        cache_unkey(a, __ldg(a.keys + __ldg(a.seg_starts + u0 - 1)), &pset, &prow);
+        leader = pset != set;
+      }
+    }
+    if (!leader) continue;
+    // runs [u0, u1) belong to this set
+    int u1 = static_cast<int>(u0) + 1;
+    while (u1 < U) {
+      uint32_t s2, r2;
+      cache_unkey(a, __ldg(a.keys + __ldg(a.seg_starts + u1)), &s2, &r2);
+      if (s2 != set) break;
+      ++u1;
+    }
+    const int slot = static_cast<int>(set) * ways + way;
+    int32_t tag = a.tags[slot], used = a.last_use[slot], cnt = a.use_count[slot];
+    int hit_lookups = 0, hit_rows = 0, uncached = 0;
+    // pass 1: hits
+    for (int u = static_cast<int>(u0); u < u1; ++u) {
+      uint32_t s2, r2;
+      const int start = __ldg(a.seg_starts + u);
+      cache_unkey(a, __ldg(a.keys + start), &s2, &r2);
+      const unsigned hit = __ballot_sync(gmask, tag == static_cast<int32_t>(r2)) & gmask;
+      if (hit) {
+        if (tag == static_cast<int32_t>(r2)) {
+          used = a.now;
+          cnt += 1;
+        }
+        const int hway = (__ffs(hit) - 1) & (ways - 1);
+        if (way == 0) {
+          a.run_loc[u] = static_cast<int>(set) * ways + hway;
+          const int end = (u + 1 < U) ? __ldg(a.seg_starts + u + 1) : a.N;
+          hit_lookups += end - start;
+          hit_rows += 1;
+        }
+      } else if (way == 0) {
+        a.run_loc[u] = -2;  // miss, decided in pass 2
+      }
+    }
+    __syncwarp(gmask);
+    // pass 2: misses claim a way, ascending row order
+    for (int u = static_cast<int>(u0); u < u1; ++u) {
+      const int state = a.run_loc[u];  // written by way 0 of this group above
+      if (state != -2) continue;
+      uint32_t s2, r2;
+      cache_unkey(a, __ldg(a.keys + __ldg(a.seg_starts + u)), &s2, &r2);
+      // candidate order: empty ways first, then by policy, ties to the lowest way
+      const bool free_now = used < a.now || tag < 0;
+      const uint32_t prio = tag < 0 ? 0u : (a.policy == kLRU ? static_cast<uint32_t>(used) + 1u
+                                                             : static_cast<uint32_t>(cnt) + 1u);
+      uint64_t cand = free_now ? ((static_cast<uint64_t>(prio) << 8) | static_cast<uint64_t>(way)) : ~0ull;
+      for (int m = 1; m < ways; m <<= 1) {
+        const uint64_t other = __shfl_xor_sync(gmask, cand, m);
+        cand = other < cand ? other : cand;
+      }
+      if (cand == ~0ull) {
+        if (way == 0) {
+          a.run_loc[u] = -1;
+          uncached += 1;
+        }
+        continue;
+      }
+      const int vway = static_cast<int>(cand & 0xff);
+      if (way == vway) {
+        const int c = atomicAdd(a.counters + 2, 1);
+        a.claims[c] = make_int4(slot, tag, static_cast<int>(r2), 0);
+        tag = static_cast<int32_t>(r2);
+        used = a.now;
+        cnt = 1;
+        a.run_loc[u] = slot;
+      }
+      __syncwarp(gmask);
+    }
+    a.tags[slot] = tag;
+    a.last_use[slot] = used;
+    a.use_count[slot] = cnt;
+    if (way == 0) {
+      if (hit_lookups) atomicAdd(a.counters + 3, hit_lookups);
+      if (hit_rows) atomicAdd(a.counters + 4, hit_rows);
+      if (uncached) atomicAdd(a.counters + 5, uncached);
+    }
+  }
+}
+
+template <int VB>
+__global__ void __launch_bounds__(256) cache_fill_kernel(const CacheArgs a, int64_t row_bytes) {
+  const int lane = threadIdx.x & 31;
+  const int nclaims = a.counters[2];
+  const int64_t wstride = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  for (int64_t c = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); c < nclaims;
+       c += wstride) {
+    const int4 cl = a.claims[c];
+    char* crow = static_cast<char*>(a.cache_rows) + static_cast<int64_t>(cl.x) * row_bytes;
+    if (cl.y >= 0 && a.dirty[cl.x]) {
+      char* hrow = static_cast<char*>(a.host_rows) + static_cast<int64_t>(cl.y) * row_bytes;
+      for (int v = lane; v < a.nvec; v += 32) st_row<VB>(hrow + v * VB, ld_rw<VB>(crow + v * VB));
+    }
+    __syncwarp();
+    const char* nrow = static_cast<const char*>(a.host_rows) + static_cast<int64_t>(cl.z) * row_bytes;
+    for (int v = lane; v < a.nvec; v += 32) st_row<VB>(crow + v * VB, ld_rw<VB>(nrow + v * VB));
+    if (lane == 0) a.dirty[cl.x] = 0;
+  }
+}
+
+__global__ void __launch_bounds__(256) cache_locate_kernel(const CacheArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int U = a.counters[0];
+  const int64_t wstride = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  for (int64_t u = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); u < U; u += wstride) {
+    const int s = __ldg(a.seg_starts + u);
+    const int e = (u + 1 < U) ? __ldg(a.seg_starts + u + 1) : a.N;
+    const int where = a.run_loc[u];
+    for (int i = s + lane; i < e; i += 32) {
+      a.loc_sorted[i] = where;
+      a.loc[__ldg(a.vals + i)] = where;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ cached forward / backward
+struct CachedRowArgs {
+  const void* cache_rows;
+  const void* host_rows;
+  const int32_t* table_offsets;
+  const int32_t* indices;
+  const int32_t* offsets;
+  const int32_t* loc;
+  void* out;
+  int32_t B, T, D, nvec, mean;
+};
+
+template <typename T, int VB>
+__global__ void __launch_bounds__(256) cached_forward_kernel(const CachedRowArgs a) {
+  using acc_t = typename Acc<T>::type;
+  constexpr int NE = VB / sizeof(T);
+  const int lane = threadIdx.x & 31;
+  const int64_t nbags = static_cast<int64_t>(a.B) * a.T;
+  const int64_t wstride = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  const int64_t row_bytes = static_cast<int64_t>(a.D) * sizeof(T);
+  for (int64_t bag = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); bag < nbags;
+       bag += wstride) {
+    const int t = static_cast<int>(bag / a.B);
+    const int b = static_cast<int>(bag - static_cast<int64_t>(t) * a.B);
+    const uint32_t row0 = static_cast<uint32_t>(__ldg(a.table_offsets + t));
+    const int s = __ldg(a.offsets + bag), e = __ldg(a.offsets + bag + 1);
+    char* out = static_cast<char*>(a.out) + (static_cast<int64_t>(b) * a.T + t) * row_bytes;
+    for (int v = lane; v < a.nvec || v == lane; v += 32) {
+      const bool vact = v < a.nvec;
+      acc_t acc[NE];
+#pragma unroll
+      for (int k = 0; k < NE; ++k) acc[k] = 0;
+      for (int p = s; p < e; ++p) {
+        const int where = __ldg(a.loc + p);
+        const char* row = where >= 0
+                              ? static_cast<const char*>(a.cache_rows) + static_cast<int64_t>(where) * row_bytes
+                              : static_cast<const char*>(a.host_rows) +
+                                    static_cast<int64_t>(row0 + static_cast<uint32_t>(__ldg(a.indices + p))) * row_bytes;
+        if (vact) {
+          acc_t x[NE];
+          unpack<T, VB>(ld_rw<VB>(row + static_cast<int64_t>(v) * VB), x);
+#pragma unroll
+          for (int k = 0; k < NE; ++k) acc[k] += x[k];
+        }
+      }
+      if (a.mean && e > s) {
+#pragma unroll
+        for (int k = 0; k < NE; ++k) acc[k] = acc[k] / static_cast<acc_t>(e - s);
+      }
+      if (vact) st_row<VB>(out + static_cast<int64_t>(v) * VB, pack_rn<T, VB>(acc));
+    }
+  }
+}
+
+struct CachedSgdArgs {
+  void* cache_rows;
+  void* host_rows;
+  uint8_t* dirty;
+  const void* grad;
+  int64_t stride_b, stride_t;
+  const uint32_t* keys;
+  const int32_t* vals;
+  const int32_t* seg_starts;
+  const int32_t* counters;
+  const int32_t* entry_bag;
+  const int32_t* loc_sorted;
+  const int32_t* offsets;
+  int32_t B, D, N, nvec, mean;
+  int32_t num_sets, Q;
+  FastDiv div_q;
+  float lr;
+};
+
+template <typename T, int VB>
+__global__ void __launch_bounds__(256) cached_sgd_kernel(const CachedSgdArgs a) {
+  using acc_t = typename Acc<T>::type;
+  constexpr int NE = VB / sizeof(T);
+  const int lane = threadIdx.x & 31;
+  const int U = __ldg(a.counters);
+  const int64_t wstride = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  const int64_t row_bytes = static_cast<int64_t>(a.D) * sizeof(T);
+  for (int64_t run = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); run < U;
+       run += wstride) {
+    const int s = __ldg(a.seg_starts + run);
+    const int e = (run + 1 < U) ? __ldg(a.seg_starts + run + 1) : a.N;
+    const int where = __ldg(a.loc_sorted + s);
+    char* w;
+    if (where >= 0) {
+      w = static_cast<char*>(a.cache_rows) + static_cast<int64_t>(where) * row_bytes;
+      if (lane == 0) a.dirty[where] = 1;
+    } else {
+      const uint32_t key = __ldg(a.keys + s);
+      const uint32_t set = fastdiv(key, a.div_q);
+      const uint32_t row = (key - set * static_cast<uint32_t>(a.Q)) * static_cast<uint32_t>(a.num_sets) + set;
+      w = static_cast<char*>(a.host_rows) + static_cast<int64_t>(row) * row_bytes;
+    }
+    for (int v = lane; v < a.nvec; v += 32) {
+      acc_t acc[NE];
+#pragma unroll
+      for (int k = 0; k < NE; ++k) acc[k] = 0;
+      for (int i = s; i < e; ++i) {
+        const int bag = __ldg(a.entry_bag + __ldg(a.vals + i));
+        const int t = bag / a.B;
+        const int b = bag - t * a.B;
+        acc_t g[NE];
+        unpack<T, VB>(ld_stream<VB>(static_cast<const char*>(a.grad) +
+                                    (static_cast<int64_t>(b) * a.stride_b + static_cast<int64_t>(t) * a.stride_t) *
+                                        static_cast<int64_t>(sizeof(T)) +
+                                    static_cast<int64_t>(v) * VB),
+                      g);
+        acc_t scale = 1;
+        if (a.mean) scale = acc_t(1) / static_cast<acc_t>(__ldg(a.offsets + bag + 1) - __ldg(a.offsets + bag));
+#pragma unroll
+        for (int k = 0; k < NE; ++k) acc[k] += g[k] * scale;
+      }
+      acc_t x[NE];
+      unpack<T, VB>(ld_rw<VB>(w + static_cast<int64_t>(v) * VB), x);
+#pragma unroll
+      for (int k = 0; k < NE; ++k) x[k] -= acc[k] * static_cast<acc_t>(a.lr);
+      st_row<VB>(w + static_cast<int64_t>(v) * VB, pack_rn<T, VB>(x));
+    }
+  }
+}
+
+template <int VB>
+__global__ void __launch_bounds__(256) cache_flush_kernel(void* cache_rows, void* host_rows, const int32_t* tags,
+                                                         uint8_t* dirty, int64_t slots, int64_t row_bytes, int nvec) {
+  const int lane = threadIdx.x & 31;
+  const int64_t wstride = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  for (int64_t slot = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); slot < slots;
+       slot += wstride) {
+    const int tag = tags[slot];
+    if (tag < 0 || !dirty[slot]) continue;
+    const char* c = static_cast<const char*>(cache_rows) + slot * row_bytes;
+    char* h = static_cast<char*>(host_rows) + static_cast<int64_t>(tag) * row_bytes;
+    for (int v = lane; v < nvec; v += 32) st_row<VB>(h + v * VB, ld_rw<VB>(c + v * VB));
+    __syncwarp();
+    if (lane == 0) dirty[slot] = 0;
+  }
+}
+
+// Scratch layout: the sort workspace of the backward followed by the cache's own arrays.
+struct CacheScratch {
+  Workspace ws;
+  int32_t* run_loc;
+  int32_t* loc_sorted;
+  int4* claims;
+  size_t total;
+};
+
+int carve_cache(void* base, int64_t N, int64_t total_rows, CacheScratch* cs) {
+  int rc = carve(base, N, total_rows, &cs->ws);
+  if (rc != TBE_OK) return rc;
+  char* p = static_cast<char*>(base);
+  size_t off = align_up(cs->ws.total, 256);
+  auto take = [&](size_t bytes) {
+    void* r = p ? p + off : nullptr;
+    off += align_up(bytes, 256);
+    return r;
+  };
+  const size_t n = static_cast<size_t>(N > 0 ? N : 1);
+  cs->run_loc = static_cast<int32_t*>(take(n * 4));
+  cs->loc_sorted = static_cast<int32_t*>(take(n * 4));
+  cs->claims = static_cast<int4*>(take(n * sizeof(int4)));
+  cs->total = off;
+  return TBE_OK;
+}
+
+int grid_for(int64_t warps) {
+  int64_t blocks = (warps + 7) / 8;
+  const int64_t cap = static_cast<int64_t>(device_sm_count()) * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return static_cast<int>(blocks);
+}
+
+int vector_bytes(const char* who, int64_t D, int dtype, const void* p0, const void* p1, const void* p2, int* vb,
+                 int* nvec) {
+  const RowGeom g = make_geom(D, dtype, p0, p1);
+  int v = g.vb;
+  if (reinterpret_cast<uintptr_t>(p2) % 16 != 0) v = 8;
+  if (v == 8 && dtype != TBE_F16) return fail(TBE_ERR_INVALID_ARGUMENT, "%s: rows must be 16-byte aligned", who);
+  if (v == 8 && (reinterpret_cast<uintptr_t>(p0) % 8 || reinterpret_cast<uintptr_t>(p1) % 8 ||
+                 reinterpret_cast<uintptr_t>(p2) % 8))
+    return fail(TBE_ERR_INVALID_ARGUMENT, "%s: rows must be 8-byte aligned", who);
+  *vb = v;
+  *nvec = static_cast<int>(D * elem_size(dtype) / v);
+  return TBE_OK;
+}
+
+}  // namespace
+}  // namespace tbe
+
+extern "C" int64_t tbe_cache_workspace_bytes(int64_t N, int64_t total_rows) {
+  if (N < 0 || total_rows <= 0) return tbe::fail(TBE_ERR_INVALID_ARGUMENT, "tbe_cache_workspace_bytes: bad sizes");
+  tbe::CacheScratch cs;
+  const int rc = tbe::carve_cache(nullptr, N, total_rows, &cs);
+  if (rc != TBE_OK) return rc;
+  return static_cast<int64_t>(cs.total);
+}
+
+extern "C" int tbe_cache_prefetch(void* cache_rows, int32_t* tags, int32_t* last_use, int32_t* use_count,
+                                  uint8_t* dirty, void* host_rows, const int32_t* table_offsets,
+                                  const int32_t* indices, const int32_t* offsets, int32_t* locations,
+                                  int32_t* stats, int64_t T, int64_t B, int64_t D, int64_t N, int64_t total_rows,
+                                  int64_t num_sets, int ways, int dtype, int policy, int now, void* workspace,
+                                  int64_t workspace_bytes, void* stream_v) {
+  using namespace tbe;
+  const char* who = "tbe_cache_prefetch";
+  TBE_REQUIRE(cache_rows && tags && last_use && use_count && dirty && host_rows && table_offsets && offsets &&
+                  locations && stats && (indices || N == 0),
+              "%s: null pointer argument", who);
+  int rc = check_sizes(who, T, B, N, total_rows);
+  if (rc != TBE_OK) return rc;
+  TBE_REQUIRE(D > 0 && D % 4 == 0, "%s: D must be a positive multiple of 4", who);
+  TBE_REQUIRE(ways >= 1 && ways <= 32 && (ways & (ways - 1)) == 0, "%s: ways must be a power of two <= 32", who);
+  TBE_REQUIRE(num_sets >= 1 && num_sets * ways < (1ll << 31), "%s: bad num_sets", who);
+  TBE_REQUIRE(policy == kLRU || policy == kLFU, "%s: policy must be 0 (LRU) or 1 (LFU)", who);
+  TBE_REQUIRE(now > 0, "%s: the step counter must start at 1", who);
+  const int64_t Q = (total_rows + num_sets - 1) / num_sets;
+  TBE_REQUIRE(num_sets * Q < (1ll << 32), "%s: num_sets * ceil(total_rows / num_sets) must fit 32 bits", who);
+  TBE_REQUIRE(workspace != nullptr && reinterpret_cast<uintptr_t>(workspace) % 256 == 0,
+              "%s: workspace must be non-null and 256-byte aligned", who);
+  CacheScratch cs;
+  rc = carve_cache(workspace, N, total_rows, &cs);
+  if (rc != TBE_OK) return rc;
+  if (static_cast<int64_t>(cs.total) > workspace_bytes)
+    return fail(TBE_ERR_WORKSPACE_TOO_SMALL, "%s: workspace has %lld bytes, %lld needed", who,
+                (long long)workspace_bytes, (long long)cs.total);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  TBE_CUDA_TRY(cudaMemsetAsync(cs.ws.counters, 0, 64, stream));
+  if (N == 0) {
+    TBE_CUDA_TRY(cudaMemsetAsync(stats, 0, 16, stream));
+    return TBE_OK;
+  }
+  int vb = 16, nvec = 0;
+  rc = vector_bytes(who, D, dtype, cache_rows, host_rows, nullptr, &vb, &nvec);
+  if (rc != TBE_OK) return rc;
+
+  CacheArgs a{};
+  a.cache_rows = cache_rows;
+  a.tags = tags;
+  a.last_use = last_use;
+  a.use_count = use_count;
+  a.dirty = dirty;
+  a.host_rows = host_rows;
+  a.table_offsets = table_offsets;
+  a.indices = indices;
+  a.offsets = offsets;
+  a.keys_in = cs.ws.keys_in;
+  a.vals_in = cs.ws.vals_in;
+  a.keys = cs.ws.keys;
+  a.vals = cs.ws.vals;
+  a.seg_starts = cs.ws.seg_starts;
+  a.counters = cs.ws.counters;
+  a.entry_bag = cs.ws.entry_bag;
+  a.run_loc = cs.run_loc;
+  a.claims = cs.claims;
+  a.loc = locations;
+  a.loc_sorted = cs.loc_sorted;
+  a.B = static_cast<int32_t>(B);
+  a.T = static_cast<int32_t>(T);
+  a.D = static_cast<int32_t>(D);
+  a.N = static_cast<int32_t>(N);
+  a.num_sets = static_cast<int32_t>(num_sets);
+  int wl = 0;
+  while ((1 << wl) < ways) ++wl;
+  a.ways_log2 = wl;
+  a.Q = static_cast<int32_t>(Q);
+  a.div_sets = make_fastdiv(static_cast<uint32_t>(num_sets));
+  a.div_q = make_fastdiv(static_cast<uint32_t>(Q));
+  a.now = now;
+  a.policy = policy;
+  a.nvec = nvec;
+
+  {
+    KernelTimer timer("cache_keys_kernel", stream);
+    cache_keys_kernel<<<grid_for(T * B), 256, 0, stream>>>(a);
+  }
+  TBE_CHECK_LAUNCH("cache_keys_kernel");
+  int bits = 1;
+  while (bits < 32 && (1ll << bits) < num_sets * Q) ++bits;
+  rc = sort_pairs(cs.ws, N, bits, stream);
+  if (rc != TBE_OK) return rc;
+  rc = select_run_starts(cs.ws, N, stream);
+  if (rc != TBE_OK) return rc;
+  {
+    KernelTimer timer("cache_update_kernel", stream);
+    const int gpw = 32 / ways;
+    cache_update_kernel<<<grid_for((N + gpw - 1) / gpw), 256, 0, stream>>>(a);
+  }
+  TBE_CHECK_LAUNCH("cache_update_kernel");
+  const int64_t row_bytes = D * elem_size(dtype);
+  {
+    KernelTimer timer("cache_fill_kernel", stream);
+    if (vb == 16) {
+      cache_fill_kernel<16><<<grid_for(N), 256, 0, stream>>>(a, row_bytes);
+    } else {
+      cache_fill_kernel<8><<<grid_for(N), 256, 0, stream>>>(a, row_bytes);
+    }
+  }
+  TBE_CHECK_LAUNCH("cache_fill_kernel");
+  {
+    KernelTimer timer("cache_locate_kernel", stream);
+    cache_locate_kernel<<<grid_for(N), 256, 0, stream>>>(a);
+  }
+  TBE_CHECK_LAUNCH("cache_locate_kernel");
+  // stats: {distinct rows, rows fetched into the cache, lookups served by rows already cached,
+  //         distinct rows already cached, distinct rows left uncached}
+  TBE_CUDA_TRY(cudaMemcpyAsync(stats, cs.ws.counters, 4, cudaMemcpyDeviceToDevice, stream));
+  TBE_CUDA_TRY(cudaMemcpyAsync(stats + 1, cs.ws.counters + 2, 16, cudaMemcpyDeviceToDevice, stream));
+  return TBE_OK;
+}
+
+extern "C" int tbe_cache_forward(const void* cache_rows, const void* host_rows, const int32_t* table_offsets,
+                                 const int32_t* indices, const int32_t* offsets, const int32_t* locations,
+                                 void* output, int64_t T, int64_t B, int64_t D, int dtype, int pooling,
+                                 void* stream_v) {
+  using namespace tbe;
+  const char* who = "tbe_cache_forward";
+  TBE_REQUIRE(cache_rows && host_rows && table_offsets && offsets && output, "%s: null pointer argument", who);
+  TBE_REQUIRE(T > 0 && B > 0 && D > 0 && D % 4 == 0 && T * B < (1ll << 31), "%s: bad sizes", who);
+  TBE_REQUIRE(pooling == TBE_POOL_SUM || pooling == TBE_POOL_MEAN, "%s: bad pooling", who);
+  int vb = 16, nvec = 0;
+  int rc = vector_bytes(who, D, dtype, cache_rows, host_rows, output, &vb, &nvec);
+  if (rc != TBE_OK) return rc;
+  CachedRowArgs a{};
+  a.cache_rows = cache_rows;
+  a.host_rows = host_rows;
+  a.table_offsets = table_offsets;
+  a.indices = indices;
+  a.offsets = offsets;
+  a.loc = locations;
+  a.out = output;
+  a.B = static_cast<int32_t>(B);
+  a.T = static_cast<int32_t>(T);
+  a.D = static_cast<int32_t>(D);
+  a.nvec = nvec;
+  a.mean = pooling == TBE_POOL_MEAN;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  {
+    KernelTimer timer("cached_forward_kernel", stream);
+    const int grid = grid_for(T * B);
+    if (dtype == TBE_F16 && vb == 16) cached_forward_kernel<__half, 16><<<grid, 256, 0, stream>>>(a);
+    else if (dtype == TBE_F16) cached_forward_kernel<__half, 8><<<grid, 256, 0, stream>>>(a);
+    else if (dtype == TBE_F32) cached_forward_kernel<float, 16><<<grid, 256, 0, stream>>>(a);
+    else return fail(TBE_ERR_UNSUPPORTED, "%s: fp16 and fp32 tables only", who);
+  }
+  TBE_CHECK_LAUNCH("cached_forward_kernel");
+  return TBE_OK;
+}
+
+extern "C" int tbe_cache_backward_sgd(const void* grad_output, int64_t stride_b, int64_t stride_t, void* cache_rows,
+                                      void* host_rows, uint8_t* dirty, const int32_t* offsets, int64_t T, int64_t B,
+                                      int64_t D, int64_t N, int64_t total_rows, int64_t num_sets, int dtype,
+                                      int pooling, float lr, void* workspace, int64_t workspace_bytes,
+                                      void* stream_v) {
+  using namespace tbe;
+  const char* who = "tbe_cache_backward_sgd";
+  TBE_REQUIRE(grad_output && cache_rows && host_rows && dirty && offsets && workspace, "%s: null pointer argument", who);
+  int rc = check_sizes(who, T, B, N, total_rows);
+  if (rc != TBE_OK) return rc;
+  TBE_REQUIRE(D > 0 && D % 4 == 0 && num_sets >= 1, "%s: bad sizes", who);
+  if (N == 0) return TBE_OK;
+  CacheScratch cs;
+  rc = carve_cache(workspace, N, total_rows, &cs);
+  if (rc != TBE_OK) return rc;
+  if (static_cast<int64_t>(cs.total) > workspace_bytes)
+    return fail(TBE_ERR_WORKSPACE_TOO_SMALL, "%s: workspace has %lld bytes, %lld needed", who,
+                (long long)workspace_bytes, (long long)cs.total);
+  int vb = 16, nvec = 0;
+  rc = vector_bytes(who, D, dtype, cache_rows, host_rows, grad_output, &vb, &nvec);
+  if (rc != TBE_OK) return rc;
+  const int es = elem_size(dtype);
+  if ((stride_b * es) % vb != 0 || (stride_t * es) % vb != 0)
+    return fail(TBE_ERR_INVALID_ARGUMENT, "%s: grad_output strides must keep rows %d-byte aligned", who, vb);
+  const int64_t Q = (total_rows + num_sets - 1) / num_sets;
+  CachedSgdArgs a{};
+  a.cache_rows = cache_rows;
+  a.host_rows = host_rows;
+  a.dirty = dirty;
+  a.grad = grad_output;
+  a.stride_b = stride_b;
+  a.stride_t = stride_t;
+  a.keys = cs.ws.keys;
+  a.vals = cs.ws.vals;
+  a.seg_starts = cs.ws.seg_starts;
+  a.counters = cs.ws.counters;
+  a.entry_bag = cs.ws.entry_bag;
+  a.loc_sorted = cs.loc_sorted;
+  a.offsets = offsets;
+  a.B = static_cast<int32_t>(B);
+  a.D = static_cast<int32_t>(D);
+  a.N = static_cast<int32_t>(N);
+  a.nvec = nvec;
+  a.mean = pooling == TBE_POOL_MEAN;
+  a.num_sets = static_cast<int32_t>(num_sets);
+  a.Q = static_cast<int32_t>(Q);
+  a.div_q = make_fastdiv(static_cast<uint32_t>(Q));
+  a.lr = lr;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  {
+    KernelTimer timer("cached_sgd_kernel", stream);
+    const int grid = grid_for(N);
+    if (dtype == TBE_F16 && vb == 16) cached_sgd_kernel<__half, 16><<<grid, 256, 0, stream>>>(a);
+    else if (dtype == TBE_F16) cached_sgd_kernel<__half, 8><<<grid, 256, 0, stream>>>(a);
+    else if (dtype == TBE_F32) cached_sgd_kernel<float, 16><<<grid, 256, 0, stream>>>(a);
+    else return fail(TBE_ERR_UNSUPPORTED, "%s: fp16 and fp32 tables only", who);
+  }
+  TBE_CHECK_LAUNCH("cached_sgd_kernel");
+  return TBE_OK;
+}
+
+extern "C" int tbe_cache_flush(void* cache_rows, void* host_rows, const int32_t* tags, uint8_t* dirty,
+                               int64_t num_slots, int64_t D, int dtype, void* stream_v) {
+  using namespace tbe;
+  const char* who = "tbe_cache_flush";
+  TBE_REQUIRE(cache_rows && host_rows && tags && dirty && num_slots > 0 && D > 0 && D % 4 == 0,
+              "%s: bad arguments", who);
+  int vb = 16, nvec = 0;
+  int rc = vector_bytes(who, D, dtype, cache_rows, host_rows, nullptr, &vb, &nvec);
+  if (rc != TBE_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const int64_t row_bytes = D * elem_size(dtype);
+  {
+    KernelTimer timer("cache_flush_kernel", stream);
+    if (vb == 16) {
+      cache_flush_kernel<16><<<grid_for(num_slots), 256, 0, stream>>>(cache_rows, host_rows, tags, dirty, num_slots,
+                                                                       row_bytes, nvec);
+    } else {
+      cache_flush_kernel<8><<<grid_for(num_slots), 256, 0, stream>>>(cache_rows, host_rows, tags, dirty, num_slots,
+                                                                      row_bytes, nvec);
+    }
+  }
+  TBE_CHECK_LAUNCH("cache_flush_kernel");
+  return TBE_OK;
+}

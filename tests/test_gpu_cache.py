@@ -1,0 +1,104 @@
+"""The LXU cache on the GPU: slot bookkeeping exactly equal to the CPU model, and transparency (the
+cached module computes what the uncached module and the per-table EmbeddingBag oracle compute)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import tbe_oracle as oracle
+from sparse_ads_baselines_b200 import table_batched_embeddings_ops as ops
+from sparse_ads_baselines_b200.lxu_cache import LXUCachedEmbeddingBags
+
+pytestmark = pytest.mark.gpu
+
+
+def _batch(rng, T, E, B, Lmax, zipf=None):
+    lengths = rng.integers(0, Lmax + 1, size=(T, B))
+    offsets = oracle.offsets_from_lengths(lengths)
+    n = int(offsets[-1])
+    if zipf:
+        idx = (rng.zipf(zipf, size=n).astype(np.int64) % E).astype(np.int32)
+    else:
+        idx = rng.integers(0, E, size=n).astype(np.int32)
+    return idx, offsets
+
+
+@pytest.mark.parametrize("policy", ["lru", "lfu"])
+@pytest.mark.parametrize("ways", [1, 2, 4, 8])
+def test_slot_bookkeeping_matches_cpu_model(cuda_device, policy, ways):
+    """Tags, last-use steps, use counts, per-lookup locations and hit counters equal the CPU model
+    exactly, step after step, with a cache small enough that sets overflow and rows stay uncached."""
+    T, E, D, B, Lmax = 3, 40, 8, 6, 5
+    cache_rows = 8 * ways
+    m = LXUCachedEmbeddingBags(T, E, D, cache_rows=cache_rows, ways=ways, policy=policy, learning_rate=0.0)
+    model = oracle.LXUCacheModel(cache_rows // ways, ways, policy)
+    to = [t * E for t in range(T)]
+    rng = np.random.default_rng(ways * 10 + (policy == "lfu"))
+    saw_uncached = saw_eviction = False
+    for step in range(8):
+        idx, off = _batch(rng, T, E, B, Lmax, zipf=1.3 if step % 2 else None)
+        m._prefetch(torch.from_numpy(idx).cuda(), torch.from_numpy(off).cuda())
+        loc, stats = model.step(to, idx, off)
+        assert np.array_equal(m._locations[:len(idx)].cpu().numpy(), loc), "locations, step %d" % step
+        assert np.array_equal(m.tags.cpu().numpy(), model.tags), "tags, step %d" % step
+        assert np.array_equal(m.last_use.cpu().numpy(), model.last_use), "last_use, step %d" % step
+        assert np.array_equal(m.use_count.cpu().numpy(), model.use_count), "use_count, step %d" % step
+        got = m.last_stats()
+        for k in ("lookups", "rows", "fetched", "hit_lookups", "hit_rows", "uncached"):
+            assert got[k] == stats[k], (k, got, stats)
+        saw_uncached |= stats["uncached"] > 0
+        saw_eviction |= step > 0 and stats["fetched"] > 0
+    assert saw_eviction
+    if ways <= 2:
+        assert saw_uncached  # tiny associativity: some set overflowed
+
+
+@pytest.mark.parametrize("fp16", [False, True])
+@pytest.mark.parametrize("pooling", ["sum", "mean"])
+def test_cached_module_is_transparent(cuda_device, fp16, pooling):
+    """Several fwd + SGD steps through a small cache (evictions, write-backs, uncached rows) give the
+    outputs and the final table of the uncached device-resident module and of the oracle."""
+    T, E, D, B, Lmax, lr = 3, 60, 32, 8, 6, 0.05
+    dtype = torch.float16 if fp16 else torch.float32
+    torch.manual_seed(0)
+    plain = ops.TableBatchedEmbeddingBags(T, E, D, optimizer=ops.Optimizer.SGD, learning_rate=lr, fp16=fp16,
+                                          pooling_mode=pooling).cuda()
+    plain.embedding_weights.data.uniform_(-1, 1)
+    cached = LXUCachedEmbeddingBags(T, E, D, cache_rows=16, ways=4, policy="lru", learning_rate=lr, fp16=fp16,
+                                    pooling_mode=pooling)
+    cached.embedding_weights.data.copy_(plain.embedding_weights.data)
+    w_ref = plain.embedding_weights.detach().cpu().clone()
+    to = [t * E for t in range(T)]
+    rng = np.random.default_rng(3)
+    tol = dict(rtol=1e-2, atol=1e-2) if fp16 else dict(rtol=1e-5, atol=1e-5)
+    for step in range(6):
+        idx, off = _batch(rng, T, E, B, Lmax, zipf=1.2 if step % 2 else None)
+        idx_d, off_d = torch.from_numpy(idx).cuda(), torch.from_numpy(off).cuda()
+        go = torch.randn(B, T, D, device="cuda").to(dtype)
+        out_p = plain(idx_d, off_d)
+        out_c = cached(idx_d, off_d)
+        ref = oracle.forward(w_ref, to, idx, off, None, pooling, compute_dtype=torch.float32)
+        torch.testing.assert_close(out_c.float().cpu(), ref.float(), **tol)
+        torch.testing.assert_close(out_c.float(), out_p.detach().float(), **tol)
+        out_p.backward(go)
+        out_c.backward(go)
+        w_ref = oracle.sgd_step(w_ref, to, idx, off, go.cpu(), lr, pooling, compute_dtype=torch.float32)
+    assert cached.dirty.any()
+    sd = cached.state_dict()  # flushes the dirty rows
+    assert not cached.dirty.any()
+    torch.testing.assert_close(sd["embedding_weights"].float().cpu(), w_ref.float(), **tol)
+    torch.testing.assert_close(sd["embedding_weights"].float().cpu(), plain.embedding_weights.detach().float().cpu(),
+                               **tol)
+
+
+def test_hit_rate_grows_with_reuse(cuda_device):
+    """Zipf lookups through a cache larger than the hot set: after a few steps most lookups hit."""
+    T, E, D, B, L = 4, 5000, 16, 64, 20
+    m = LXUCachedEmbeddingBags(T, E, D, cache_rows=4096, ways=4, policy="lru", learning_rate=0.0)
+    rng = np.random.default_rng(0)
+    rates = []
+    for step in range(6):
+        idx = (rng.zipf(1.2, size=T * B * L).astype(np.int64) % E).astype(np.int32)
+        off = (np.arange(T * B + 1) * L).astype(np.int32)
+        m(torch.from_numpy(idx).cuda(), torch.from_numpy(off).cuda())
+        rates.append(m.last_stats()["hit_rate"])
+    assert rates[0] == 0.0 and rates[-1] > 0.5, rates
