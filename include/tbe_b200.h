@@ -86,6 +86,16 @@ TBE_API int tbe_forward(const void* weights, const int32_t* table_offsets,
                 int64_t T, int64_t B, int64_t D, int dtype, int pooling,
                 void* stream);
 
+/* tbe_forward into a wider output: sample b's row of table t starts at
+ * output + b*out_stride_b + t*D (elements), out_stride_b >= T*D.  It lets tables of
+ * different width share one [B][sum D] output, one call per width.
+ * replaces table_batched_embeddings_cuda.cu:945-1004 (batched_embedding_forward_mixed_D_cuda)
+ * together with the per-table loop of the mixed-D op layer. */
+TBE_API int tbe_forward_strided(const void* weights, const int32_t* table_offsets,
+                const int32_t* indices, const int32_t* offsets,
+                const void* per_sample_weights, void* output, int64_t out_stride_b,
+                int64_t T, int64_t B, int64_t D, int dtype, int pooling, void* stream);
+
 /* Table-sharded forward with the all-to-all fused into the store: this rank owns
  * T local tables (global columns t0 .. t0+T of T_total) and looks up the GLOBAL
  * batch B for them; sample b belongs to rank b / (B / world) and its pooled row is
@@ -269,9 +279,12 @@ TBE_API int tbe_free_host_mapped(void* host_ptr);
  *   use_count  int32 [num_sets*ways]  steps that looked the row up since it was inserted (0)
  *   dirty      uint8 [num_sets*ways]  row differs from the host copy (0)
  *   host_rows  [total_rows][D]  the table, in device-mapped pinned host memory
- * Placement: row r lives in set r % num_sets.  Per step (now = 1, 2, ...): every distinct
+ * Placement: row r lives in set mix(r) % num_sets, where mix is a fixed bijection of the
+ * 31-bit row ids (two rounds of x ^= x >> 16; x = x * 0x45d9f3b mod 2^31; then x ^= x >> 16),
+ * so that rows a table size apart do not collide; "ascending order" below means ascending
+ * mix(r).  Per step (now = 1, 2, ...): every distinct
  * row of the batch is looked up first (a hit refreshes last_use and use_count); then the
- * misses of a set claim, in ascending row order, a way that was not used in this step --
+ * misses of a set claim, in ascending order, a way that was not used in this step --
  * an empty one first, else the one with the smallest last_use (policy 0, LRU) or the
  * smallest use_count (policy 1, LFU), ties to the lowest way; a dirty victim is written
  * back to host_rows and the new row is fetched.  A row whose set has no free way stays

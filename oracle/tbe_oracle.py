@@ -280,9 +280,10 @@ class LXUCacheModel:
     """CPU model of the set-associative row cache (no counterpart in the reference: parity unpinned
     by it; this model IS the specification the CUDA cache is compared with, slot by slot).
 
-    Row r lives in set ``r % num_sets``.  Per step, with ``now`` = 1, 2, ...: every distinct row of
+    Row r lives in set ``mix(r) % num_sets`` where ``mix`` is a fixed bijection of 31-bit ids (so that
+    rows a table-size apart do not collide); "ascending order" below is ascending ``mix(r)``.  Per step, with ``now`` = 1, 2, ...: every distinct row of
     the batch is looked up first -- a hit sets ``last_use = now`` and adds one to ``use_count`` --
-    then the misses of each set, in ascending row order, claim a way with ``last_use < now`` (or an
+    then the misses of each set, in ascending mixed-id order, claim a way with ``last_use < now`` (or an
     empty one): empty ways first, then the smallest ``last_use`` (LRU) or the smallest
     ``use_count`` (LFU), ties to the lowest way.  A claimed way gets ``last_use = now``,
     ``use_count = 1``.  A miss with no claimable way stays uncached for the step (location -1)."""
@@ -293,6 +294,19 @@ class LXUCacheModel:
         self.last_use = np.zeros(num_sets * ways, dtype=np.int32)
         self.use_count = np.zeros(num_sets * ways, dtype=np.int32)
         self.now = 0
+
+    @staticmethod
+    def mix(r):
+        x = int(r) & 0x7FFFFFFF
+        x ^= x >> 16
+        x = (x * 0x45D9F3B) & 0x7FFFFFFF
+        x ^= x >> 16
+        x = (x * 0x45D9F3B) & 0x7FFFFFFF
+        x ^= x >> 16
+        return x
+
+    def set_of(self, r):
+        return self.mix(r) % self.num_sets
 
     def step(self, table_offsets, indices, offsets):
         """Returns (locations int32 [N], stats dict) for one batch and updates the model."""
@@ -308,7 +322,7 @@ class LXUCacheModel:
         hit_lookups = hit_rows = 0
         by_set = {}
         for r, c in zip(uniq.tolist(), counts.tolist()):
-            by_set.setdefault(r % self.num_sets, []).append((r, c))
+            by_set.setdefault(self.set_of(r), []).append((r, c))
         fetched = uncached = 0
         for s, members in by_set.items():
             base = s * self.ways
@@ -324,7 +338,7 @@ class LXUCacheModel:
                     hit_rows += 1
                 else:
                     misses.append(r)
-            for r in sorted(misses):
+            for r in sorted(misses, key=self.mix):
                 best = None
                 for w in range(self.ways):
                     slot = base + w

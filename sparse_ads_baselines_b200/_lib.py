@@ -26,6 +26,7 @@ SIGNATURES = {
     "tbe_kernel_timing_enable": (_i32, [_i32]),
     "tbe_kernel_timing_read": (_i64, [ctypes.c_char_p, _i64]),
     "tbe_forward": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
+    "tbe_forward_strided": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _i32, _vp]),
     "tbe_forward_sharded": (_i32, [_vp, _vp, _vp, _vp, _vp, ctypes.POINTER(_vp), _i32, _i64, _i64, _i64, _i64,
                                    _i64, _i32, _i32, _vp]),
     "tbe_all2all_push": (_i32, [_vp, ctypes.POINTER(_vp), _i32, _i32, _i64, _i64, _vp]),

@@ -3,15 +3,15 @@
 // The table lives in pinned, device-mapped host memory (every uncached access crosses the host
 // link); `ways * num_sets` rows of it are kept in HBM.  Once per step, before the lookup:
 //
-//   1. cache_keys_kernel  : key[p] = (row % num_sets) * Q + row / num_sets for every lookup p
-//                           (Q = ceil(total_rows / num_sets); a bijection of the row id that sorts
-//                           by set first, then by row), value[p] = p
+//   1. cache_keys_kernel  : h = mix(row), a fixed bijection of the 31-bit row ids; the row's set is
+//                           h % num_sets; key[p] = set * Q + h / num_sets (Q = ceil(2^31 / num_sets):
+//                           sorts by set first, equal keys <=> equal rows), value[p] = p
 //   2. radix sort + run starts (CUB): equal rows adjacent, the rows of one set adjacent and
 //                           ascending
 //   3. cache_update_kernel: one lane group per set touched this step, one lane per way holding that
 //                           way's tag / last-use / use-count in registers.  First every distinct
 //                           row of the set is looked up (a hit refreshes the way), then the misses
-//                           claim, in ascending row order, the least-recently (LRU) or
+//                           claim, in ascending key order, the least-recently (LRU) or
 //                           least-frequently (LFU) used way not used in this step; ties go to the
 //                           lowest way.  If no way is free the row stays uncached for this step.
 //   4. cache_fill_kernel  : one warp per claimed way: the dirty victim row is written back to the
@@ -48,6 +48,7 @@ struct CacheArgs {
   int32_t* counters;    // [0] runs, [2] claims, [3] hit lookups, [4] hit rows, [5] uncached rows
   int32_t* entry_bag;   // bag of every position
   int32_t* run_loc;     // per run: slot or -1
+  int32_t* run_row;     // per run: the row id
   int4* claims;         // {slot, old_tag, new_row, 0}
   int32_t* loc;         // per position: slot or -1 (output)
   int32_t* loc_sorted;  // per sorted entry: slot or -1
@@ -58,16 +59,29 @@ struct CacheArgs {
   int32_t nvec;
 };
 
+// A bijection of the 31-bit row ids (xor-shifts and odd multiplications are each invertible modulo
+// 2^31).  Rows that differ by a multiple of the table size, or by any other regular stride, would
+// otherwise fall into the same set whenever that stride shares a factor with num_sets.
+__device__ __forceinline__ uint32_t mix_row(uint32_t x) {
+  x ^= x >> 16;
+  x = (x * 0x45d9f3bu) & 0x7fffffffu;
+  x ^= x >> 16;
+  x = (x * 0x45d9f3bu) & 0x7fffffffu;
+  x ^= x >> 16;
+  return x;
+}
+// Sort key: set first, then the rest of the mixed id -- equal keys <=> equal rows.
 __device__ __forceinline__ uint32_t cache_key(const CacheArgs& a, uint32_t row) {
-  const uint32_t q = fastdiv(row, a.div_sets);
-  const uint32_t set = row - q * static_cast<uint32_t>(a.num_sets);
+  const uint32_t h = mix_row(row);
+  const uint32_t q = fastdiv(h, a.div_sets);
+  const uint32_t set = h - q * static_cast<uint32_t>(a.num_sets);
   return set * static_cast<uint32_t>(a.Q) + q;
 }
-__device__ __forceinline__ void cache_unkey(const CacheArgs& a, uint32_t key, uint32_t* set, uint32_t* row) {
-  const uint32_t s = fastdiv(key, a.div_q);
-  const uint32_t q = key - s * static_cast<uint32_t>(a.Q);
-  *set = s;
-  *row = q * static_cast<uint32_t>(a.num_sets) + s;
+__device__ __forceinline__ uint32_t key_set(const CacheArgs& a, uint32_t key) { return fastdiv(key, a.div_q); }
+// The row a sorted entry looks up, recomputed from its index position.
+__device__ __forceinline__ uint32_t row_of_position(const CacheArgs& a, int pos) {
+  const int bag = __ldg(a.entry_bag + pos);
+  return static_cast<uint32_t>(__ldg(a.table_offsets + bag / a.B)) + static_cast<uint32_t>(__ldg(a.indices + pos));
 }
 
 __global__ void __launch_bounds__(256) cache_keys_kernel(const CacheArgs a) {
@@ -102,33 +116,23 @@ __global__ void __launch_bounds__(256) cache_update_kernel(const CacheArgs a) {
        u0 - (lane >> a.ways_log2) < U; u0 += gstride) {
     // (the loop bound is warp-uniform; groups past the end idle)
     bool leader = false;
-    uint32_t set = 0, row = 0;
+    uint32_t set = 0;
     if (u0 < U) {
-      cache_unkey(a, __ldg(a.keys + __ldg(a.seg_starts + u0)), &set, &row);
-      leader = true;
-      if (u0 > 0) {
-        uint32_t pset, prow;
-        cache_unkey(a, __ldg(a.keys + __ldg(a.seg_starts + u0 - 1)), &pset, &prow);
-        leader = pset != set;
-      }
+      set = key_set(a, __ldg(a.keys + __ldg(a.seg_starts + u0)));
+      leader = u0 == 0 || key_set(a, __ldg(a.keys + __ldg(a.seg_starts + u0 - 1))) != set;
     }
     if (!leader) continue;
     // runs [u0, u1) belong to this set
     int u1 = static_cast<int>(u0) + 1;
-    while (u1 < U) {
-      uint32_t s2, r2;
-      cache_unkey(a, __ldg(a.keys + __ldg(a.seg_starts + u1)), &s2, &r2);
-      if (s2 != set) break;
-      ++u1;
-    }
+    while (u1 < U && key_set(a, __ldg(a.keys + __ldg(a.seg_starts + u1))) == set) ++u1;
     const int slot = static_cast<int>(set) * ways + way;
     int32_t tag = a.tags[slot], used = a.last_use[slot], cnt = a.use_count[slot];
     int hit_lookups = 0, hit_rows = 0, uncached = 0;
     // pass 1: hits
     for (int u = static_cast<int>(u0); u < u1; ++u) {
-      uint32_t s2, r2;
       const int start = __ldg(a.seg_starts + u);
-      cache_unkey(a, __ldg(a.keys + start), &s2, &r2);
+      const uint32_t r2 = row_of_position(a, __ldg(a.vals + start));
+      if (way == 0) a.run_row[u] = static_cast<int32_t>(r2);
       const unsigned hit = __ballot_sync(gmask, tag == static_cast<int32_t>(r2)) & gmask;
       if (hit) {
         if (tag == static_cast<int32_t>(r2)) {
@@ -151,8 +155,7 @@ __global__ void __launch_bounds__(256) cache_update_kernel(const CacheArgs a) {
     for (int u = static_cast<int>(u0); u < u1; ++u) {
       const int state = a.run_loc[u];  // written by way 0 of this group above
       if (state != -2) continue;
-      uint32_t s2, r2;
-      cache_unkey(a, __ldg(a.keys + __ldg(a.seg_starts + u)), &s2, &r2);
+      const uint32_t r2 = static_cast<uint32_t>(a.run_row[u]);
       // candidate order: empty ways first, then by policy, ties to the lowest way
       const bool free_now = used < a.now || tag < 0;
       const uint32_t prio = tag < 0 ? 0u : (a.policy == kLRU ? static_cast<uint32_t>(used) + 1u
@@ -292,12 +295,30 @@ struct CachedSgdArgs {
   const int32_t* counters;
   const int32_t* entry_bag;
   const int32_t* loc_sorted;
+  const int32_t* run_row;
   const int32_t* offsets;
+  int2* long_list;      // runs longer than kLongCachedRun, handled by a whole CTA each
+  int32_t* long_count;
   int32_t B, D, N, nvec, mean;
-  int32_t num_sets, Q;
-  FastDiv div_q;
+  int32_t lpr_log2;     // lanes per row in the long-run kernel
   float lr;
 };
+
+constexpr int kLongCachedRun = 64;
+
+// Gradient row of a bag, vector v, and 1/L of the bag for mean pooling.
+template <typename T, int VB>
+__device__ __forceinline__ Raw<VB> cached_grad(const CachedSgdArgs& a, int bag, int v, typename Acc<T>::type* scale) {
+  using acc_t = typename Acc<T>::type;
+  const int t = bag / a.B;
+  const int b = bag - t * a.B;
+  *scale = 1;
+  if (a.mean) *scale = acc_t(1) / static_cast<acc_t>(__ldg(a.offsets + bag + 1) - __ldg(a.offsets + bag));
+  return ld_stream<VB>(static_cast<const char*>(a.grad) +
+                       (static_cast<int64_t>(b) * a.stride_b + static_cast<int64_t>(t) * a.stride_t) *
+                           static_cast<int64_t>(sizeof(T)) +
+                       static_cast<int64_t>(v) * VB);
+}
 
 template <typename T, int VB>
 __global__ void __launch_bounds__(256) cached_sgd_kernel(const CachedSgdArgs a) {
@@ -311,16 +332,17 @@ __global__ void __launch_bounds__(256) cached_sgd_kernel(const CachedSgdArgs a) 
        run += wstride) {
     const int s = __ldg(a.seg_starts + run);
     const int e = (run + 1 < U) ? __ldg(a.seg_starts + run + 1) : a.N;
+    if (e - s > kLongCachedRun) {  // a hot row: queued for the CTA-per-run kernel
+      if (lane == 0) a.long_list[atomicAdd(a.long_count, 1)] = make_int2(static_cast<int>(run), 0);
+      continue;
+    }
     const int where = __ldg(a.loc_sorted + s);
     char* w;
     if (where >= 0) {
       w = static_cast<char*>(a.cache_rows) + static_cast<int64_t>(where) * row_bytes;
       if (lane == 0) a.dirty[where] = 1;
     } else {
-      const uint32_t key = __ldg(a.keys + s);
-      const uint32_t set = fastdiv(key, a.div_q);
-      const uint32_t row = (key - set * static_cast<uint32_t>(a.Q)) * static_cast<uint32_t>(a.num_sets) + set;
-      w = static_cast<char*>(a.host_rows) + static_cast<int64_t>(row) * row_bytes;
+      w = static_cast<char*>(a.host_rows) + static_cast<int64_t>(__ldg(a.run_row + run)) * row_bytes;
     }
     for (int v = lane; v < a.nvec; v += 32) {
       acc_t acc[NE];
@@ -350,6 +372,77 @@ __global__ void __launch_bounds__(256) cached_sgd_kernel(const CachedSgdArgs a) 
   }
 }
 
+// One CTA per queued long run: lane groups of lpr lanes take every G-th lookup of the run, four in
+// flight each; the groups' partial sums are folded in group order in shared memory, so the result
+// does not depend on scheduling.
+template <typename T, int VB>
+__global__ void __launch_bounds__(256) cached_sgd_long_kernel(const CachedSgdArgs a) {
+  using acc_t = typename Acc<T>::type;
+  constexpr int NE = VB / sizeof(T);
+  __shared__ acc_t part[256 * NE];
+  const int lpr = 1 << a.lpr_log2;
+  const int sub = threadIdx.x & (lpr - 1);
+  const int gid = threadIdx.x >> a.lpr_log2;
+  const int G = blockDim.x >> a.lpr_log2;
+  const int U = __ldg(a.counters);
+  const int nlong = *a.long_count;
+  const int64_t row_bytes = static_cast<int64_t>(a.D) * sizeof(T);
+  for (int li = blockIdx.x; li < nlong; li += gridDim.x) {
+    const int run = a.long_list[li].x;
+    const int s = __ldg(a.seg_starts + run);
+    const int e = (run + 1 < U) ? __ldg(a.seg_starts + run + 1) : a.N;
+    const int where = __ldg(a.loc_sorted + s);
+    char* w = where >= 0 ? static_cast<char*>(a.cache_rows) + static_cast<int64_t>(where) * row_bytes
+                         : static_cast<char*>(a.host_rows) + static_cast<int64_t>(__ldg(a.run_row + run)) * row_bytes;
+    if (threadIdx.x == 0 && where >= 0) a.dirty[where] = 1;
+    for (int c = 0; c * lpr < a.nvec; ++c) {
+      const int v = c * lpr + sub;
+      const bool vact = v < a.nvec;
+      acc_t acc[NE];
+#pragma unroll
+      for (int k = 0; k < NE; ++k) acc[k] = 0;
+      for (int i = s + gid; i < e; i += 4 * G) {
+        int bag[4];
+        Raw<VB> r[4];
+        acc_t sc[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) bag[u] = (i + u * G < e) ? __ldg(a.entry_bag + __ldg(a.vals + i + u * G)) : -1;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          r[u] = raw_zero<VB>();
+          sc[u] = 1;
+          if (bag[u] >= 0 && vact) r[u] = cached_grad<T, VB>(a, bag[u], v, &sc[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          acc_t g[NE];
+          unpack<T, VB>(r[u], g);
+#pragma unroll
+          for (int k = 0; k < NE; ++k) acc[k] += g[k] * sc[u];
+        }
+      }
+      __syncthreads();  // the previous chunk's partial sums have been consumed
+#pragma unroll
+      for (int k = 0; k < NE; ++k) part[threadIdx.x * NE + k] = acc[k];
+      __syncthreads();
+      if (gid == 0 && vact) {
+        acc_t tot[NE];
+#pragma unroll
+        for (int k = 0; k < NE; ++k) tot[k] = 0;
+        for (int g = 0; g < G; ++g) {
+#pragma unroll
+          for (int k = 0; k < NE; ++k) tot[k] += part[(g * lpr + sub) * NE + k];
+        }
+        acc_t x[NE];
+        unpack<T, VB>(ld_rw<VB>(w + static_cast<int64_t>(v) * VB), x);
+#pragma unroll
+        for (int k = 0; k < NE; ++k) x[k] -= tot[k] * static_cast<acc_t>(a.lr);
+        st_row<VB>(w + static_cast<int64_t>(v) * VB, pack_rn<T, VB>(x));
+      }
+    }
+  }
+}
+
 template <int VB>
 __global__ void __launch_bounds__(256) cache_flush_kernel(void* cache_rows, void* host_rows, const int32_t* tags,
                                                          uint8_t* dirty, int64_t slots, int64_t row_bytes, int nvec) {
@@ -371,6 +464,7 @@ __global__ void __launch_bounds__(256) cache_flush_kernel(void* cache_rows, void
 struct CacheScratch {
   Workspace ws;
   int32_t* run_loc;
+  int32_t* run_row;
   int32_t* loc_sorted;
   int4* claims;
   size_t total;
@@ -388,6 +482,7 @@ int carve_cache(void* base, int64_t N, int64_t total_rows, CacheScratch* cs) {
   };
   const size_t n = static_cast<size_t>(N > 0 ? N : 1);
   cs->run_loc = static_cast<int32_t*>(take(n * 4));
+  cs->run_row = static_cast<int32_t*>(take(n * 4));
   cs->loc_sorted = static_cast<int32_t*>(take(n * 4));
   cs->claims = static_cast<int4*>(take(n * sizeof(int4)));
   cs->total = off;
@@ -445,8 +540,8 @@ extern "C" int tbe_cache_prefetch(void* cache_rows, int32_t* tags, int32_t* last
   TBE_REQUIRE(num_sets >= 1 && num_sets * ways < (1ll << 31), "%s: bad num_sets", who);
   TBE_REQUIRE(policy == kLRU || policy == kLFU, "%s: policy must be 0 (LRU) or 1 (LFU)", who);
   TBE_REQUIRE(now > 0, "%s: the step counter must start at 1", who);
-  const int64_t Q = (total_rows + num_sets - 1) / num_sets;
-  TBE_REQUIRE(num_sets * Q < (1ll << 32), "%s: num_sets * ceil(total_rows / num_sets) must fit 32 bits", who);
+  const int64_t Q = ((1ll << 31) + num_sets - 1) / num_sets;  // mixed row ids span 31 bits
+  TBE_REQUIRE(num_sets * Q < (1ll << 32), "%s: num_sets too large for 32-bit sort keys", who);
   TBE_REQUIRE(workspace != nullptr && reinterpret_cast<uintptr_t>(workspace) % 256 == 0,
               "%s: workspace must be non-null and 256-byte aligned", who);
   CacheScratch cs;
@@ -483,6 +578,7 @@ extern "C" int tbe_cache_prefetch(void* cache_rows, int32_t* tags, int32_t* last
   a.counters = cs.ws.counters;
   a.entry_bag = cs.ws.entry_bag;
   a.run_loc = cs.run_loc;
+  a.run_row = cs.run_row;
   a.claims = cs.claims;
   a.loc = locations;
   a.loc_sorted = cs.loc_sorted;
@@ -602,7 +698,6 @@ extern "C" int tbe_cache_backward_sgd(const void* grad_output, int64_t stride_b,
   const int es = elem_size(dtype);
   if ((stride_b * es) % vb != 0 || (stride_t * es) % vb != 0)
     return fail(TBE_ERR_INVALID_ARGUMENT, "%s: grad_output strides must keep rows %d-byte aligned", who, vb);
-  const int64_t Q = (total_rows + num_sets - 1) / num_sets;
   CachedSgdArgs a{};
   a.cache_rows = cache_rows;
   a.host_rows = host_rows;
@@ -622,11 +717,15 @@ extern "C" int tbe_cache_backward_sgd(const void* grad_output, int64_t stride_b,
   a.N = static_cast<int32_t>(N);
   a.nvec = nvec;
   a.mean = pooling == TBE_POOL_MEAN;
-  a.num_sets = static_cast<int32_t>(num_sets);
-  a.Q = static_cast<int32_t>(Q);
-  a.div_q = make_fastdiv(static_cast<uint32_t>(Q));
+  a.run_row = cs.run_row;
+  a.long_list = cs.ws.long_list;
+  a.long_count = cs.ws.counters + 1;
+  int lpr_log2 = 0;
+  while ((1 << lpr_log2) < nvec && lpr_log2 < 5) ++lpr_log2;
+  a.lpr_log2 = lpr_log2;
   a.lr = lr;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  TBE_CUDA_TRY(cudaMemsetAsync(cs.ws.counters + 1, 0, 4, stream));  // the long-run queue starts empty
   {
     KernelTimer timer("cached_sgd_kernel", stream);
     const int grid = grid_for(N);
@@ -636,6 +735,14 @@ extern "C" int tbe_cache_backward_sgd(const void* grad_output, int64_t stride_b,
     else return fail(TBE_ERR_UNSUPPORTED, "%s: fp16 and fp32 tables only", who);
   }
   TBE_CHECK_LAUNCH("cached_sgd_kernel");
+  {
+    KernelTimer timer("cached_sgd_long_kernel", stream);
+    const int grid = device_sm_count() * 2;
+    if (dtype == TBE_F16 && vb == 16) cached_sgd_long_kernel<__half, 16><<<grid, 256, 0, stream>>>(a);
+    else if (dtype == TBE_F16) cached_sgd_long_kernel<__half, 8><<<grid, 256, 0, stream>>>(a);
+    else cached_sgd_long_kernel<float, 16><<<grid, 256, 0, stream>>>(a);
+  }
+  TBE_CHECK_LAUNCH("cached_sgd_long_kernel");
   return TBE_OK;
 }
 

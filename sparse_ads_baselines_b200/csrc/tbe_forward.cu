@@ -23,6 +23,7 @@ struct FwdArgs {
   int32_t B, T, D;
   int32_t B_local, T_total, t0;
   int32_t lpr_log2, nvec, nchunks;
+  int64_t out_stride_b_bytes;  // distance between the output rows of consecutive samples (unsharded)
 };
 
 template <typename T>
@@ -87,7 +88,8 @@ __global__ void __launch_bounds__(256) tbe_forward_kernel(const FwdArgs a) {
       outp = static_cast<char*>(a.out[dest]) +
              (static_cast<int64_t>(bl) * a.T_total + a.t0 + t) * static_cast<int64_t>(row_bytes);
     } else {
-      outp = static_cast<char*>(a.out[0]) + (static_cast<int64_t>(b) * a.T + t) * static_cast<int64_t>(row_bytes);
+      outp = static_cast<char*>(a.out[0]) + static_cast<int64_t>(b) * a.out_stride_b_bytes +
+             static_cast<int64_t>(t) * static_cast<int64_t>(row_bytes);
     }
 
     for (int c = 0; c < a.nchunks; ++c) {
@@ -224,7 +226,7 @@ int dispatch_fwd(const FwdArgs& a, int dtype, int vb, bool weighted, bool mean, 
 int forward_common(const void* weights, const int32_t* table_offsets, const int32_t* indices,
                    const int32_t* offsets, const void* psw, void* const* outs, int world,
                    int64_t T, int64_t B, int64_t D, int64_t T_total, int64_t t0, int dtype,
-                   int pooling, bool sharded, void* stream) {
+                   int pooling, bool sharded, int64_t out_stride_b, void* stream) {
   // `indices` may be null when every bag is empty: it is only read inside non-empty bag extents
   TBE_REQUIRE(weights && table_offsets && offsets && outs, "tbe_forward: null pointer argument");
   TBE_REQUIRE(T > 0, "tbe_forward: T must be > 0 (got %lld)", (long long)T);
@@ -257,6 +259,11 @@ int forward_common(const void* weights, const int32_t* table_offsets, const int3
   a.B_local = static_cast<int32_t>(B / world);
   a.T_total = static_cast<int32_t>(T_total);
   a.t0 = static_cast<int32_t>(t0);
+  if (out_stride_b <= 0) out_stride_b = T * D;
+  TBE_REQUIRE(out_stride_b >= T * D, "tbe_forward: output sample stride %lld is smaller than T*D", (long long)out_stride_b);
+  a.out_stride_b_bytes = out_stride_b * elem_size(dtype);
+  if (a.out_stride_b_bytes % 16 != 0) align_probe = reinterpret_cast<const void*>(uintptr_t(8));
+  TBE_REQUIRE(a.out_stride_b_bytes % 8 == 0, "tbe_forward: output sample stride must keep rows 8-byte aligned");
   const RowGeom g = make_geom(D, dtype, weights, align_probe);
   TBE_REQUIRE(g.vb == 16 || dtype == TBE_F16, "tbe_forward: weights/output must be 16-byte aligned");
   if (g.vb == 8) {
@@ -282,7 +289,16 @@ extern "C" int tbe_forward(const void* weights, const int32_t* table_offsets, co
                            int64_t T, int64_t B, int64_t D, int dtype, int pooling, void* stream) {
   void* outs[1] = {output};
   return tbe::forward_common(weights, table_offsets, indices, offsets, per_sample_weights, outs, 1, T, B, D,
-                             T, 0, dtype, pooling, false, stream);
+                             T, 0, dtype, pooling, false, 0, stream);
+}
+
+extern "C" int tbe_forward_strided(const void* weights, const int32_t* table_offsets, const int32_t* indices,
+                                   const int32_t* offsets, const void* per_sample_weights, void* output,
+                                   int64_t out_stride_b, int64_t T, int64_t B, int64_t D, int dtype, int pooling,
+                                   void* stream) {
+  void* outs[1] = {output};
+  return tbe::forward_common(weights, table_offsets, indices, offsets, per_sample_weights, outs, 1, T, B, D,
+                             T, 0, dtype, pooling, false, out_stride_b, stream);
 }
 
 extern "C" int tbe_forward_sharded(const void* weights, const int32_t* table_offsets,
@@ -291,5 +307,5 @@ extern "C" int tbe_forward_sharded(const void* weights, const int32_t* table_off
                                    int64_t T, int64_t B, int64_t D, int64_t T_total, int64_t t0,
                                    int dtype, int pooling, void* stream) {
   return tbe::forward_common(weights, table_offsets, indices, offsets, per_sample_weights, peer_outputs,
-                             world, T, B, D, T_total, t0, dtype, pooling, true, stream);
+                             world, T, B, D, T_total, t0, dtype, pooling, true, 0, stream);
 }

@@ -298,6 +298,123 @@ def backward_approx_adagrad(grad_output, weights, table_offsets, indices, offset
     return grad_psw
 
 
+# ---------------------------------------------------------------------------- mixed-D tables
+# Tables of different width and height share one flat weights vector (reference:
+# MixedDimTableBatchedEmbeddingBags, table_batched_embeddings_ops.py:324-434).  Each table is run
+# through the uniform kernels as a one-table problem: its lookups are a contiguous slice of
+# `indices`, its rows a contiguous slice of `weights`, and its pooled rows go straight into its
+# columns of the [B, sum(D)] output (tbe_forward_strided) / are read from its columns of the
+# gradient (strided backward), so nothing is copied.
+
+_host_copies = {}
+
+
+def _host_list(t):
+    key = (t.data_ptr(), t.numel(), t._version)
+    v = _host_copies.get(key)
+    if v is None:
+        if len(_host_copies) > 256:
+            _host_copies.clear()
+        v = [int(x) for x in t.detach().cpu().tolist()]
+        _host_copies[key] = v
+    return v
+
+
+_zero_offsets = {}
+
+
+def _one_table_offsets(device):
+    z = _zero_offsets.get(device.index)
+    if z is None:
+        z = torch.zeros(1, dtype=torch.int32, device=device)
+        _zero_offsets[device.index] = z
+    return z
+
+
+def _mixed_tables(weights, table_offsets, dim_offsets, indices, offsets):
+    """Yields (t, weights_t [E_t, D_t], indices_t, offsets_t, lo, hi, col0, D_t) per table."""
+    _check_cuda("weights", weights)
+    _require(weights.dim() == 1 and weights.is_contiguous(), "mixed-D weights must be a flat contiguous vector")
+    _check_cuda("indices", indices, torch.int32)
+    _check_cuda("offsets", offsets, torch.int32)
+    elem = _host_list(table_offsets)
+    cols = _host_list(dim_offsets)
+    T = len(cols) - 1
+    _require(len(elem) == T + 1, "table_offsets and dim_offsets must both have T + 1 entries")
+    _require((offsets.numel() - 1) % T == 0, "offsets must have T*B+1 entries")
+    B = (offsets.numel() - 1) // T
+    bounds = offsets[::B].cpu().tolist()  # first lookup of every table (+ the total); one synchronisation
+    out = []
+    for t in range(T):
+        D = cols[t + 1] - cols[t]
+        _require(D > 0 and D % 4 == 0, "every embedding dimension must be a positive multiple of 4")
+        w_t = weights[elem[t]:elem[t + 1]].view(-1, D)
+        lo, hi = int(bounds[t]), int(bounds[t + 1])
+        out.append((t, w_t, indices[lo:hi], offsets[t * B:(t + 1) * B + 1] - lo, lo, hi, cols[t], D))
+    return out, B, T
+
+
+def forward_mixed_D(weights, table_offsets, dim_offsets, total_D, indices, offsets, indice_weights, L_max,
+                    BT_block_size, shmem):
+    """Pooled lookup over tables of different width: returns ``[B, total_D]`` (reference:
+    batched_embedding_forward_mixed_D_cuda, table_batched_embeddings_cuda.cu:945-1004)."""
+    tables, B, T = _mixed_tables(weights, table_offsets, dim_offsets, indices, offsets)
+    dev = weights.device
+    out = torch.empty((B, int(total_D)), dtype=weights.dtype, device=dev)
+    es = weights.element_size()
+    with torch.cuda.device(dev):
+        for (t, w_t, idx_t, off_t, lo, hi, col0, D) in tables:
+            psw = indice_weights[lo:hi].contiguous() if indice_weights is not None else None
+            _lib.call("tbe_forward_strided", w_t.data_ptr(), _one_table_offsets(dev).data_ptr(), idx_t.data_ptr(),
+                      off_t.data_ptr(), psw.data_ptr() if psw is not None else None, out.data_ptr() + col0 * es,
+                      int(total_D), 1, B, D, _DTYPES[weights.dtype], _POOLING["sum"], _stream(dev))
+    return out
+
+
+def _backward_mixed(exact, grad_output, weights, table_offsets, table_dim_offsets, dim_offsets, total_D, indices,
+                    offsets, indice_weights, optimizer_state, learning_rate, eps, stochastic_rounding):
+    tables, B, T = _mixed_tables(weights, table_offsets, dim_offsets, indices, offsets)
+    rows = _host_list(table_dim_offsets)
+    _require(tuple(grad_output.shape) == (B, int(total_D)), "grad_output must be [B, total_D]")
+    if grad_output.stride(1) != 1:
+        grad_output = grad_output.contiguous()
+    grad_psw = None
+    if indice_weights is not None:
+        grad_psw = torch.empty(indices.shape, dtype=grad_output.dtype, device=weights.device)
+    to1 = _one_table_offsets(weights.device)
+    for (t, w_t, idx_t, off_t, lo, hi, col0, D) in tables:
+        g_t = grad_output[:, col0:col0 + D].unsqueeze(1)  # [B, 1, D_t], sample stride total_D
+        s_t = optimizer_state[rows[t]:rows[t + 1]]
+        if exact:
+            backward_exact_adagrad(g_t, w_t, to1, idx_t, off_t, None, s_t, learning_rate, eps, stochastic_rounding, 1)
+        else:
+            psw = indice_weights[lo:hi] if indice_weights is not None else None
+            gp = backward_approx_adagrad(g_t, w_t, to1, idx_t, off_t, psw, s_t, learning_rate, eps, 200,
+                                         stochastic_rounding, 1)
+            if gp is not None:
+                grad_psw[lo:hi] = gp
+    return grad_psw
+
+
+def backward_approx_adagrad_mixed_D(grad_output, weights, table_offsets, table_dim_offsets, dim_offsets, total_D,
+                                    indices, offsets, indice_weights, optimizer_state, learning_rate, eps, L_max,
+                                    stochastic_rounding, BT_block_size):
+    """reference: batched_embedding_backward_adagrad_approx_mixed_D_cuda,
+    table_batched_embeddings_cuda.cu:1076-1163."""
+    return _backward_mixed(False, grad_output, weights, table_offsets, table_dim_offsets, dim_offsets, total_D,
+                           indices, offsets, indice_weights, optimizer_state, learning_rate, eps, stochastic_rounding)
+
+
+def backward_exact_adagrad_mixed_D(grad_output, weights, table_offsets, table_dim_offsets, dim_offsets, total_D,
+                                   indices, offsets, indice_weights, optimizer_state, learning_rate, eps,
+                                   stochastic_rounding, BT_block_size):
+    """reference: batched_embedding_backward_adagrad_exact_mixed_D_cuda,
+    table_batched_embeddings_cuda.cu:1350-1469 (per-sample weights unsupported, as there)."""
+    _require(indice_weights is None, "exact rowwise Adagrad does not support per-sample weights")
+    return _backward_mixed(True, grad_output, weights, table_offsets, table_dim_offsets, dim_offsets, total_D,
+                           indices, offsets, None, optimizer_state, learning_rate, eps, stochastic_rounding)
+
+
 def sort_segments(table_offsets, indices, offsets, total_rows):
     """The backward's integer bookkeeping: ``(sorted_rows, sorted_bags, segment_starts)`` with
     ``segment_starts`` trimmed to the number of distinct rows (synchronises to read that count)."""

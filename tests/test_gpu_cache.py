@@ -102,3 +102,30 @@ def test_hit_rate_grows_with_reuse(cuda_device):
         m(torch.from_numpy(idx).cuda(), torch.from_numpy(off).cuda())
         rates.append(m.last_stats()["hit_rate"])
     assert rates[0] == 0.0 and rates[-1] > 0.5, rates
+
+
+@pytest.mark.parametrize("fp16,D", [(False, 32), (True, 128), (False, 260)])
+def test_hot_rows_take_the_long_run_path(cuda_device, fp16, D):
+    """A few rows receive hundreds of lookups each (more than the 64 a single warp handles): the
+    CTA-per-run kernel must give the oracle's SGD update, deterministically."""
+    T, E, B, L, lr = 2, 6, 300, 3, 0.01
+    dtype = torch.float16 if fp16 else torch.float32
+    cached = LXUCachedEmbeddingBags(T, E, D, cache_rows=8, ways=4, policy="lru", learning_rate=lr, fp16=fp16)
+    torch.manual_seed(1)
+    w0 = (torch.rand(T * E, D) * 2 - 1).to(dtype)
+    rng = np.random.default_rng(5)
+    idx = rng.integers(0, E, size=T * B * L).astype(np.int32)
+    off = (np.arange(T * B + 1) * L).astype(np.int32)
+    go = (torch.randn(B, T, D) * 0.05).to(dtype)
+    results = []
+    for _ in range(2):
+        cached.embedding_weights.data.copy_(w0.cuda())
+        cached.tags.fill_(-1)
+        cached.dirty.zero_()
+        out = cached(torch.from_numpy(idx).cuda(), torch.from_numpy(off).cuda())
+        out.backward(go.cuda())
+        results.append(cached.state_dict()["embedding_weights"].float().cpu().clone())
+    ref = oracle.sgd_step(w0, [0, E], idx, off, go, lr, compute_dtype=torch.float32)
+    tol = dict(rtol=1e-2, atol=1e-2) if fp16 else dict(rtol=1e-5, atol=2e-5)
+    torch.testing.assert_close(results[0], ref.float(), **tol)
+    assert torch.equal(results[0], results[1])

@@ -65,6 +65,20 @@ def _worker(rank, world, port, exchange, dtype_name, failures):
             out.backward(grads[rank].to(dev))
             torch.cuda.synchronize()
             torch.testing.assert_close(m.tbe.embedding_weights.detach().float().cpu(), expect_w.float(), **tol)
+        if exchange == "nccl" and dtype_name == "fp32":
+            # row-wise sharding collectives, after test_sparse_embedding_cuda.py:138-171: the same seed
+            # on every rank regenerates every rank's tensor
+            from sparse_ads_baselines_b200 import sparse_embedding_cuda_ops as se_ops
+            for (b, t, d) in [(world, 1, 1), (2 * world, 8, 7), (4 * world, 3, 284)]:
+                g2 = torch.Generator().manual_seed(42)
+                parts = [torch.randn(b, t, d, generator=g2) for _ in range(world)]
+                x = parts[rank].to(dev).requires_grad_(True)
+                y = se_ops.ReduceScatterFunction.apply(x)
+                bl = b // world
+                torch.testing.assert_close(y.detach().cpu(), sum(parts)[rank * bl:(rank + 1) * bl], rtol=1e-5, atol=1e-5)
+                gy = [torch.randn(bl, t, d, generator=g2) for _ in range(world)]
+                y.backward(gy[rank].to(dev))
+                torch.testing.assert_close(x.grad.cpu(), torch.cat(gy, dim=0), rtol=0, atol=0)
     except Exception as e:
         failures.put("rank %d: %r" % (rank, e))
     finally:

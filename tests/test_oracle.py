@@ -197,20 +197,28 @@ def test_lxu_cache_model_by_hand():
     used way; a set whose ways were all used in the step leaves further rows uncached."""
     m = oracle.LXUCacheModel(num_sets=2, ways=2, policy="lru")
     to = [0]
-    def step(rows):
+    # rows by set, each list in ascending mixed-id order (the model's claim order)
+    in_set = {0: [], 1: []}
+    for r in sorted(range(64), key=m.mix):
+        in_set[m.set_of(r)].append(r)
+    a, b, c, d, e = in_set[0][:5]
+    z = in_set[1][0]
+
+    def step(model, rows):
         idx = np.asarray(rows, dtype=np.int32)
         off = np.asarray([0, len(rows)], dtype=np.int32)
-        return m.step(to, idx, off)
-    loc, st = step([0, 2, 1])                 # set 0: rows 0,2 -> ways 0,1; set 1: row 1 -> way 0
+        return model.step(to, idx, off)
+
+    loc, st = step(m, [a, b, z])               # set 0: a, b -> ways 0, 1; set 1: z -> way 0
     assert loc.tolist() == [0, 1, 2] and st["fetched"] == 3 and st["hit_lookups"] == 0
-    loc, st = step([2, 2, 4])                 # row 2 hits (twice); row 4 evicts row 0 (older)
+    loc, st = step(m, [b, b, c])               # b hits (twice); c evicts a (older)
     assert loc.tolist() == [1, 1, 0] and st["hit_lookups"] == 2 and st["hit_rows"] == 1 and st["fetched"] == 1
-    assert m.tags.tolist() == [4, 2, 1, -1]
-    loc, st = step([0, 6, 8])                 # set 0 misses 0,6,8 ascending: 0 -> way 1 (last_use 2... both used at step 2,
-    assert st["uncached"] == 1               # tie -> way 0), 6 -> the other way, 8 finds no free way
-    assert sorted(m.tags[:2].tolist()) == [0, 6] and loc.tolist()[2] == -1
+    assert m.tags.tolist() == [c, b, z, -1]
+    loc, st = step(m, [a, d, e])               # three misses, two ways (both last used at step 2: tie -> way 0
+    assert st["uncached"] == 1                 # first); the last one in claim order finds no free way
+    assert m.tags[:2].tolist() == [a, d] and loc.tolist() == [0, 1, -1]
     lfu = oracle.LXUCacheModel(num_sets=1, ways=2, policy="lfu")
     for rows in ([1, 2], [1], [1], [2]):
-        lfu.step(to, np.asarray(rows, dtype=np.int32), np.asarray([0, len(rows)], dtype=np.int32))
-    loc, _ = lfu.step(to, np.asarray([3], dtype=np.int32), np.asarray([0, 1], dtype=np.int32))
-    assert lfu.tags.tolist() == [1, 3]        # row 2 (2 uses) goes, row 1 (3 uses) stays although row 2 was used later
+        step(lfu, rows)
+    step(lfu, [3])
+    assert sorted(lfu.tags.tolist()) == [1, 3]  # row 2 (2 uses) goes, row 1 (3 uses) stays although 2 was used later
