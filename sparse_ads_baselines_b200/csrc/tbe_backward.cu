@@ -271,15 +271,13 @@ template <typename T, int VB, bool MEAN>
 __device__ __forceinline__ void add_grad(const Raw<VB>& r, typename Acc<T>::type scale, typename Acc<T>::type* acc) {
   using acc_t = typename Acc<T>::type;
   constexpr int NE = VB / sizeof(T);
-  acc_t e[NE];
-  unpack<T, VB>(r, e);
+  if (MEAN) {
+    acc_t e[NE];
+    unpack<T, VB>(r, e);
 #pragma unroll
-  for (int k = 0; k < NE; ++k) {
-    if (MEAN) {
-      acc[k] += e[k] * scale;
-    } else {
-      acc[k] += e[k];
-    }
+    for (int k = 0; k < NE; ++k) acc[k] += e[k] * scale;
+  } else {
+    accumulate<T, VB>(r, acc);
   }
 }
 

@@ -323,6 +323,33 @@ __device__ __forceinline__ void unpack<double, 16>(const Raw<16>& r, double* out
   out[1] = __hiloint2double(static_cast<int>(r.w[3]), static_cast<int>(r.w[2]));
 }
 
+// acc[k] += element k of the vector.  For fp16 rows this is Blackwell's mixed-precision add
+// (add.rn.f32.f16: fp16 operand, fp32 accumulator, one rounding): the same value as converting and
+// adding, in half the instructions -- these kernels are short of issue slots, not of FLOPs.
+template <typename T, int VB>
+__device__ __forceinline__ void accumulate(const Raw<VB>& r, typename Acc<T>::type* acc) {
+  constexpr int NE = VB / sizeof(T);
+  typename Acc<T>::type e[NE];
+  unpack<T, VB>(r, e);
+#pragma unroll
+  for (int k = 0; k < NE; ++k) acc[k] += e[k];
+}
+__device__ __forceinline__ void add_half2_to_floats(uint32_t packed, float& a0, float& a1) {
+  asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tadd.rn.f32.f16 %0, lo, %0;\n\tadd.rn.f32.f16 %1, hi, %1;\n\t}"
+      : "+f"(a0), "+f"(a1)
+      : "r"(packed));
+}
+template <>
+__device__ __forceinline__ void accumulate<__half, 16>(const Raw<16>& r, float* acc) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) add_half2_to_floats(r.w[i], acc[2 * i], acc[2 * i + 1]);
+}
+template <>
+__device__ __forceinline__ void accumulate<__half, 8>(const Raw<8>& r, float* acc) {
+#pragma unroll
+  for (int i = 0; i < 2; ++i) add_half2_to_floats(r.w[i], acc[2 * i], acc[2 * i + 1]);
+}
+
 // Round-to-nearest-even pack.
 template <typename T, int VB>
 __device__ __forceinline__ Raw<VB> pack_rn(const typename Acc<T>::type* in);

@@ -95,7 +95,8 @@ __global__ void __launch_bounds__(256) tbe_forward_kernel(const FwdArgs a) {
     for (int c = 0; c < a.nchunks; ++c) {
       const int v = (c << 5) + sub;
       const bool vact = v < a.nvec;
-      const char* const Wv = W + static_cast<int64_t>(v) * VB;  // this lane's vector of row 0
+      // this lane's vector of row 0; lanes past the end of the row re-read vector 0 and never store
+      const char* const Wv = W + (vact ? static_cast<int64_t>(v) * VB : 0);
       acc_t acc[NE];
 #pragma unroll
       for (int k = 0; k < NE; ++k) acc[k] = 0;
@@ -113,7 +114,32 @@ __global__ void __launch_bounds__(256) tbe_forward_kernel(const FwdArgs a) {
         }
         const int cnt = min(32, cur_e - base);
         const int steps = (cnt + (1 << rps_log2) - 1) >> rps_log2;
-        for (int s = 0; s < steps; s += UNROLL) {
+        // steps in which every row slot of the warp has a row: no predicates, no zero fill
+        const int full_steps = ((cnt >> rps_log2) / UNROLL) * UNROLL;
+        int s = 0;
+        for (; s < full_steps; s += UNROLL) {
+          Raw<VB> r[UNROLL];
+          acc_t w[UNROLL];
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) {
+            const int j = ((s + u) << rps_log2) + slot;
+            const int idx = __shfl_sync(kFullMask, idx_l, j);
+            if (WEIGHTED) w[u] = __shfl_sync(kFullMask, w_l, j);
+            r[u] = ld_stream<VB>(Wv + static_cast<uint64_t>(row0 + static_cast<uint32_t>(idx)) * row_bytes);
+          }
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) {
+            if (WEIGHTED) {
+              acc_t e[NE];
+              unpack<T, VB>(r[u], e);
+#pragma unroll
+              for (int k = 0; k < NE; ++k) acc[k] += e[k] * w[u];
+            } else {
+              accumulate<T, VB>(r[u], acc);
+            }
+          }
+        }
+        for (; s < steps; s += UNROLL) {
           Raw<VB> r[UNROLL];
           acc_t w[UNROLL];
 #pragma unroll
@@ -121,7 +147,7 @@ __global__ void __launch_bounds__(256) tbe_forward_kernel(const FwdArgs a) {
             const int j = ((s + u) << rps_log2) + slot;
             const int idx = __shfl_sync(kFullMask, idx_l, j & 31);
             if (WEIGHTED) w[u] = __shfl_sync(kFullMask, w_l, j & 31);
-            if (j < cnt && vact) {
+            if (j < cnt) {
               // 32-bit row id times 32-bit row size: one wide multiply-add per address
               r[u] = ld_stream<VB>(Wv + static_cast<uint64_t>(row0 + static_cast<uint32_t>(idx)) * row_bytes);
             } else {
@@ -130,15 +156,13 @@ __global__ void __launch_bounds__(256) tbe_forward_kernel(const FwdArgs a) {
           }
 #pragma unroll
           for (int u = 0; u < UNROLL; ++u) {
-            acc_t e[NE];
-            unpack<T, VB>(r[u], e);
+            if (WEIGHTED) {
+              acc_t e[NE];
+              unpack<T, VB>(r[u], e);
 #pragma unroll
-            for (int k = 0; k < NE; ++k) {
-              if (WEIGHTED) {
-                acc[k] += e[k] * w[u];
-              } else {
-                acc[k] += e[k];
-              }
+              for (int k = 0; k < NE; ++k) acc[k] += e[k] * w[u];
+            } else {
+              accumulate<T, VB>(r[u], acc);
             }
           }
         }
