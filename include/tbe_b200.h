@@ -226,12 +226,16 @@ TBE_API int tbe_backward_approx_rowwise_adagrad(
  * consume): row ids sorted ascending, the bag id of each sorted entry, the start of
  * each run of equal row ids and the number of runs.  Outputs are device arrays of
  * N, N, N+1 and 1 int32 (the first *num_segments entries of segment_starts are set).
+ * max_rows_per_table: as for tbe_backward_sgd (0 = unknown); with it the plan is
+ * built by the same table-segmented sort the optimizer entry points use, which
+ * requires table_offsets to ascend (table t's rows precede table t+1's).
  * replaces table_batched_embeddings_cuda.cu:1471-1497,1638-1655
  * (linear_index_weight_offsets_kernel + cub SortPairs) and the segment scan
  * at :1523-1539. */
 TBE_API int tbe_sort_segments(const int32_t* table_offsets, const int32_t* indices,
                       const int32_t* offsets,
                       int64_t T, int64_t B, int64_t N, int64_t total_rows,
+                      int64_t max_rows_per_table,
                       int32_t* sorted_rows, int32_t* sorted_bags,
                       int32_t* segment_starts, int32_t* num_segments,
                       void* workspace, int64_t workspace_bytes, void* stream);

@@ -43,7 +43,7 @@ SIGNATURES = {
     "tbe_backward_approx_rowwise_adagrad": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                                                    _i64, _i64, _i64, _i32, _f32, _f32, _i32, _u64, _u64, _i64,
                                                    _vp, _i64, _vp]),
-    "tbe_sort_segments": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
+    "tbe_sort_segments": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
     "tbe_construct_offsets": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp]),
     "tbe_check_inputs": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "tbe_alloc_managed": (_i32, [ctypes.POINTER(_vp), _i64]),

@@ -85,6 +85,11 @@ int carve(void* base, int64_t N, int64_t total_rows, Workspace* ws) {
   ws->seg_starts = static_cast<int32_t*>(take((n + 1) * 4));
   ws->entry_bag = static_cast<int32_t*>(take(n * 4));
   ws->entry_g2 = static_cast<float*>(take(n * 4));
+  ws->hist_cap = static_cast<int64_t>(n / 16 + 4096);
+  ws->queue_cap = static_cast<int64_t>(n / kBucketSortCapacity + 2);
+  ws->hist = static_cast<int32_t*>(take(ws->hist_cap * 4));
+  ws->bucket_start = static_cast<int32_t*>(take(ws->hist_cap * 4));
+  ws->oversize = static_cast<int2*>(take(ws->queue_cap * sizeof(int2)));
   ws->cub_temp = take(cub_bytes);
   ws->cub_bytes = cub_bytes;
   ws->total = off;
@@ -182,9 +187,20 @@ __global__ void __launch_bounds__(256) linearize_kernel(const int32_t* __restric
   }
 }
 
+__global__ void __launch_bounds__(256) keys_to_rows_kernel(const int32_t* __restrict__ table_offsets, int idx_bits,
+                                                          const uint32_t* __restrict__ keys,
+                                                          int32_t* __restrict__ rows, int64_t N) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (i < N) rows[i] = static_cast<int32_t>(key_to_row(table_offsets, idx_bits, keys[i]));
+}
+
 // Steps 1-2.  Leaves the sorted pairs in ws.keys / ws.vals.
 int build_plan(const int32_t* table_offsets, const int32_t* indices, const int32_t* offsets, int64_t T,
-               int64_t B, int64_t N, KeyLayout layout, Workspace& ws, cudaStream_t stream) {
+               int64_t B, int64_t N, int64_t max_rows_per_table, KeyLayout layout, Workspace& ws,
+               cudaStream_t stream) {
+  BucketGeometry geom;
+  if (bucket_geometry(T, N, max_rows_per_table, layout, ws, &geom))
+    return bucket_sort_plan(indices, offsets, T, B, N, layout, geom, ws, stream);
   const int64_t nbags = T * B;
   {
     const int wpb = 256 / 32;
@@ -899,7 +915,7 @@ int exact_backward(int opt, const void* grad, int64_t stride_b, int64_t stride_t
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   const KeyLayout layout = key_layout(T, total_rows, max_rows_per_table, false);
   if (!plan_ready) {
-    rc = build_plan(table_offsets, indices, offsets, T, B, N, layout, ws, stream);
+    rc = build_plan(table_offsets, indices, offsets, T, B, N, max_rows_per_table, layout, ws, stream);
     if (rc != TBE_OK) return rc;
   }
   TBE_CUDA_TRY(cudaMemsetAsync(ws.counters, 0, 64, stream));
@@ -968,7 +984,8 @@ extern "C" int tbe_backward_plan(const int32_t* table_offsets, const int32_t* in
   Workspace ws;
   rc = prepare_workspace(who, workspace, workspace_bytes, N, total_rows, &ws);
   if (rc != TBE_OK || N == 0) return rc;
-  return build_plan(table_offsets, indices, offsets, T, B, N, key_layout(T, total_rows, max_rows_per_table, false), ws,
+  return build_plan(table_offsets, indices, offsets, T, B, N, max_rows_per_table,
+                    key_layout(T, total_rows, max_rows_per_table, false), ws,
                     static_cast<cudaStream_t>(stream));
 }
 
@@ -997,9 +1014,10 @@ extern "C" int tbe_backward_exact_rowwise_adagrad(const void* grad_output, int64
 }
 
 extern "C" int tbe_sort_segments(const int32_t* table_offsets, const int32_t* indices, const int32_t* offsets,
-                                 int64_t T, int64_t B, int64_t N, int64_t total_rows, int32_t* sorted_rows,
-                                 int32_t* sorted_bags, int32_t* segment_starts, int32_t* num_segments,
-                                 void* workspace, int64_t workspace_bytes, void* stream_v) {
+                                 int64_t T, int64_t B, int64_t N, int64_t total_rows,
+                                 int64_t max_rows_per_table, int32_t* sorted_rows, int32_t* sorted_bags,
+                                 int32_t* segment_starts, int32_t* num_segments, void* workspace,
+                                 int64_t workspace_bytes, void* stream_v) {
   using namespace tbe;
   const char* who = "tbe_sort_segments";
   TBE_REQUIRE(table_offsets && offsets && (indices || N == 0) && sorted_rows && sorted_bags && segment_starts &&
@@ -1015,11 +1033,18 @@ extern "C" int tbe_sort_segments(const int32_t* table_offsets, const int32_t* in
     TBE_CUDA_TRY(cudaMemsetAsync(num_segments, 0, 4, stream));
     return TBE_OK;
   }
-  rc = build_plan(table_offsets, indices, offsets, T, B, N, key_layout(T, total_rows, 0, true), ws, stream);
+  const KeyLayout layout = key_layout(T, total_rows, max_rows_per_table, true);
+  rc = build_plan(table_offsets, indices, offsets, T, B, N, max_rows_per_table, layout, ws, stream);
   if (rc != TBE_OK) return rc;
   rc = select_run_starts(ws, N, stream);
   if (rc != TBE_OK) return rc;
-  TBE_CUDA_TRY(cudaMemcpyAsync(sorted_rows, ws.keys, N * 4, cudaMemcpyDeviceToDevice, stream));
+  if (layout.idx_bits > 0) {
+    keys_to_rows_kernel<<<static_cast<unsigned>((N + 255) / 256), 256, 0, stream>>>(
+        table_offsets, layout.idx_bits, ws.keys, sorted_rows, N);
+    TBE_CHECK_LAUNCH("keys_to_rows_kernel");
+  } else {
+    TBE_CUDA_TRY(cudaMemcpyAsync(sorted_rows, ws.keys, N * 4, cudaMemcpyDeviceToDevice, stream));
+  }
   TBE_CUDA_TRY(cudaMemcpyAsync(sorted_bags, ws.vals, N * 4, cudaMemcpyDeviceToDevice, stream));
   TBE_CUDA_TRY(cudaMemcpyAsync(segment_starts, ws.seg_starts, N * 4, cudaMemcpyDeviceToDevice, stream));
   TBE_CUDA_TRY(cudaMemcpyAsync(num_segments, ws.counters, 4, cudaMemcpyDeviceToDevice, stream));

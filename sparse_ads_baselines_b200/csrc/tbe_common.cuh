@@ -32,6 +32,8 @@ enum Tuning {
   kTuneFwdBlocksPerSM,
   kTuneBwdBlocksPerSM,
   kTuneBwdVpl,
+  kTuneBwdSort,     // 0: two-level bucket sort when the batch suits it, 1: always the device radix sort
+  kTuneSortBucket,  // wanted mean bucket size of the two-level sort (0: default)
   kTuneCount
 };
 

@@ -16,7 +16,11 @@ struct Workspace {
   int2* long_list;      // {first sorted position, end position} of queued runs; N/32 + 2 entries
   int32_t* entry_bag;   // N: bag id of every index position (approx backward)
   float* entry_g2;      // N: squared gradient norm applied by every index position (approx backward)
-  int32_t* counters;    // [0] = number of runs, [1] = queued long runs
+  int32_t* counters;    // [0] = number of runs, [1] = queued long runs, [8] = queued oversize buckets
+  int32_t* hist;        // bucket sort: per (table, slice) bucket histograms, hist_cap entries
+  int32_t* bucket_start;  // bucket sort: first sorted position of every (table, bucket), hist_cap entries
+  int2* oversize;       // bucket sort: {first, end} position of buckets too large for shared memory, queue_cap entries
+  int64_t hist_cap, queue_cap;
   void* cub_temp;
   size_t cub_bytes;
   size_t total;
@@ -31,6 +35,21 @@ struct KeyLayout {
 };
 
 KeyLayout key_layout(int64_t T, int64_t total_rows, int64_t max_rows_per_table, bool full_order);
+
+// Largest bucket the two-level sort finishes in shared memory.
+constexpr int kBucketSortCapacity = 2048;
+
+// Two-level sort geometry: bucket = index >> shift, nb buckets and `slices` position ranges per table.
+struct BucketGeometry {
+  int shift, nb, slices;
+};
+// False when the batch does not suit the two-level sort (no composite keys, tables too long,
+// scratch too small, or switched off): the caller then uses linearize + sort_pairs.
+bool bucket_geometry(int64_t T, int64_t N, int64_t max_rows_per_table, KeyLayout layout, const Workspace& ws,
+                     BucketGeometry* g);
+// indices/offsets -> ws.keys / ws.vals ordered by (table, index, position).
+int bucket_sort_plan(const int32_t* indices, const int32_t* offsets, int64_t T, int64_t B, int64_t N,
+                     KeyLayout layout, const BucketGeometry& g, Workspace& ws, cudaStream_t stream);
 
 // Carves the workspace; with base == nullptr only sizes are computed.
 int carve(void* base, int64_t N, int64_t total_rows, Workspace* ws);

@@ -1,0 +1,603 @@
+// Table-segmented two-level sort of the (row key, bag id) pairs of a TBE batch (sm_100a).
+//
+// The backward needs the lookups grouped by row, and inside a group ordered by bag (the order of the
+// index positions).  A generic device radix sort spends ~180 us on the 5 M pairs of the headline
+// batch, a fifth of the whole forward+backward step, although the input is far from arbitrary:
+// lookups arrive grouped by table (table t owns positions [offsets[t*B], offsets[(t+1)*B])), only
+// the index inside the table needs ordering, and a table sees far fewer lookups than it has rows.
+// This file orders every table independently in two levels that stay in L2:
+//
+//   1. bucket_count_kernel   : lookups per (table, bucket), bucket = index >> shift.
+//   2. bucket_scatter_kernel : every (slice, table) CTA reserves room in each bucket for the lookups
+//                              of its position range and moves (key, bag id) there.  The bag id of a
+//                              position comes from a running search in `offsets`, so this kernel
+//                              also replaces the separate linearize pass.  The order inside a
+//                              bucket is whatever the atomics gave; level 2 makes that irrelevant.
+//   3. bucket_rank_kernel    : one CTA per bucket.  A counting sort on the low `shift` index bits in
+//                              shared memory (one 16-bit counter per possible row of the bucket)
+//                              brings equal rows together; pairs that share a row are then ranked
+//                              by (key, bag id).  Equal pairs are indistinguishable, so the output
+//                              is the unique order by (table, index, bag): exactly what a stable
+//                              sort of the position-ordered input gives, and independent of how the
+//                              atomics of any step were served.  A bucket larger than the CTA's
+//                              capacity is queued instead ...
+//   4. oversize_sort_kernel  : ... and sorted by a 1024-thread CTA with stable 8-bit radix passes
+//                              through global memory, first on the bag id, then on the index bits.
+//                              Skewed batches, where a few hot rows put most of a table in one
+//                              bucket, land here; normally the queue is empty.
+#include <cub/block/block_scan.cuh>
+
+#include <atomic>
+
+#include "tbe_plan.cuh"
+
+namespace tbe {
+
+namespace {
+
+constexpr int kCountThreads = 512;
+constexpr int kScatterThreads = 512;
+constexpr int kScatterTile = 2048;  // positions a CTA gathers in shared memory at a time
+constexpr int kRankThreads = 256;
+constexpr int kRankItems = kBucketSortCapacity / kRankThreads;  // pairs a thread holds
+constexpr int kRankBits = 14;                                   // most index bits level 2 can count on
+constexpr int kRankWords = (1 << kRankBits) / 2;                // two 16-bit counters per word
+constexpr int kOversizeThreads = 1024;
+constexpr int kOversizeWarps = kOversizeThreads / 32;
+constexpr int kMaxDigits = 256;             // radix passes look at up to 8 bits
+constexpr int kMaxBuckets = 1024;           // buckets per table
+constexpr int kDefaultBucketTarget = 1400;  // wanted mean bucket size
+static_assert(kBucketSortCapacity % kRankThreads == 0 && kBucketSortCapacity < 65536, "16-bit positions");
+
+__device__ __forceinline__ uint32_t bucket_of(int32_t index, int shift, int nb) {
+  const uint32_t b = static_cast<uint32_t>(index) >> shift;
+  return b < static_cast<uint32_t>(nb) ? b : static_cast<uint32_t>(nb - 1);  // a bad index must not leave the histogram
+}
+
+// Position range of slice s of table t.
+__device__ __forceinline__ void slice_range(const int32_t* __restrict__ offsets, int64_t t, int32_t B, int s, int S,
+                                            int32_t* ts, int32_t* a, int32_t* b) {
+  const int32_t t0 = __ldg(offsets + t * B), t1 = __ldg(offsets + (t + 1) * B);
+  const int64_t len = t1 - t0;
+  *ts = t0;
+  *a = t0 + static_cast<int32_t>(len * s / S);
+  *b = t0 + static_cast<int32_t>(len * (s + 1) / S);
+}
+
+// Share of [a, b) that warp w of W walks: consecutive shares, each a multiple of 32 long.
+__device__ __forceinline__ void warp_share(int32_t a, int32_t b, int w, int W, int32_t* ca, int32_t* cb) {
+  const int32_t per = (((b - a) + W - 1) / W + 31) & ~31;
+  const int64_t lo = static_cast<int64_t>(a) + static_cast<int64_t>(w) * per;
+  *ca = lo < b ? static_cast<int32_t>(lo) : b;
+  *cb = lo + per < b ? static_cast<int32_t>(lo + per) : b;
+}
+
+// totals[t * nb + bucket] += lookups of slice s of table t that fall in the bucket (zeroed by the host).
+__global__ void __launch_bounds__(kCountThreads) bucket_count_kernel(const int32_t* __restrict__ indices,
+                                                                     const int32_t* __restrict__ offsets, int32_t B,
+                                                                     int shift, int nb, int32_t* __restrict__ totals) {
+  __shared__ int32_t sh[kMaxBuckets];
+  const int s = blockIdx.x, S = gridDim.x;
+  const int64_t t = blockIdx.y;
+  for (int i = threadIdx.x; i < nb; i += kCountThreads) sh[i] = 0;
+  __syncthreads();
+  int32_t ts, a, b;
+  slice_range(offsets, t, B, s, S, &ts, &a, &b);
+  for (int32_t p = a + threadIdx.x; p < b; p += kCountThreads)
+    atomicAdd(&sh[bucket_of(__ldg(indices + p), shift, nb)], 1);
+  __syncthreads();
+  for (int i = threadIdx.x; i < nb; i += kCountThreads)
+    if (sh[i]) atomicAdd(totals + t * nb + i, sh[i]);
+}
+
+// Largest bag g in [lo, hi) with offsets[g] <= p (offsets[lo] <= p is given).  All lanes call it with
+// the same arguments; each round probes 32 evenly spaced bags at once.
+__device__ __forceinline__ int32_t warp_find_bag(const int32_t* __restrict__ offsets, int32_t lo, int32_t hi,
+                                                 int32_t p, int lane) {
+  while (hi - lo > 1) {
+    const int32_t step = (hi - lo + 31) >> 5;
+    const int64_t probe = static_cast<int64_t>(lo) + static_cast<int64_t>(lane + 1) * step;
+    const bool ok = probe < hi && __ldg(offsets + probe) <= p;
+    const int c = __popc(__ballot_sync(0xffffffffu, ok));
+    lo += c * step;
+    hi = min(hi, lo + step);
+  }
+  return lo;
+}
+
+// Lane l receives the end of bag from + l, i.e. offsets[from + 1 + l], clamped to the table's last bag.
+__device__ __forceinline__ int32_t load_bag_ends(const int32_t* __restrict__ offsets, int32_t from, int32_t bag_hi,
+                                                 int lane) {
+  const int64_t i = static_cast<int64_t>(from) + 1 + lane;
+  return __ldg(offsets + (i < bag_hi ? i : bag_hi));
+}
+
+// Number of the 32 ascending values held one per lane in `ends` that are <= p (each lane its own p).
+__device__ __forceinline__ int count_not_above(int32_t ends, int32_t p) {
+  int c = 0;
+#pragma unroll
+  for (int step = 16; step >= 1; step >>= 1) {
+    const int32_t v = __shfl_sync(0xffffffffu, ends, c + step - 1);
+    if (v <= p) c += step;
+  }
+  const int32_t last = __shfl_sync(0xffffffffu, ends, 31);
+  if (c == 31 && last <= p) c = 32;
+  return c;
+}
+
+// A CTA walks its slice in tiles of kScatterTile positions.  Per tile: count the buckets (the old
+// value of a pair's counter is its slot among the tile's pairs of that bucket), reserve room for the
+// tile in every bucket with one global atomic per bucket, gather the pairs bucket by bucket in shared
+// memory, then copy them out: a bucket's share of the tile is one contiguous run of 8-byte pairs, so
+// the stores coalesce instead of costing a sector per pair.
+__global__ void __launch_bounds__(kScatterThreads, 3) bucket_scatter_kernel(
+    const int32_t* __restrict__ indices, const int32_t* __restrict__ offsets, int32_t B, int64_t T, int idx_bits,
+    int shift, int nb, const int32_t* __restrict__ totals, int32_t* __restrict__ reserved,
+    int32_t* __restrict__ bucket_start, uint2* __restrict__ pairs) {
+  __shared__ uint2 stage[kScatterTile];
+  __shared__ int32_t cnt[kMaxBuckets];     // pairs of the tile per bucket, then their first slot in `stage`
+  __shared__ int32_t delta[kMaxBuckets];   // global position minus slot in `stage`, per bucket
+  __shared__ int32_t tstart[kMaxBuckets];  // first position of every bucket of the table
+  using Scan = cub::BlockScan<int32_t, kScatterThreads>;
+  __shared__ typename Scan::TempStorage scan_tmp;
+  constexpr int kPer = kMaxBuckets / kScatterThreads;  // buckets per thread
+  constexpr int kRounds = kScatterTile / kScatterThreads;
+
+  const int s = blockIdx.x, S = gridDim.x;
+  const int64_t t = blockIdx.y;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  int32_t ts, a, b;
+  slice_range(offsets, t, B, s, S, &ts, &a, &b);
+  {
+    int32_t tot[kPer];
+    int32_t sum = 0;
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int i = threadIdx.x * kPer + j;
+      tot[j] = i < nb ? __ldg(totals + t * nb + i) : 0;
+      sum += tot[j];
+    }
+    int32_t excl;
+    Scan(scan_tmp).ExclusiveSum(sum, excl);
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int i = threadIdx.x * kPer + j;
+      if (i < nb) {
+        tstart[i] = ts + excl;
+        if (s == 0) bucket_start[t * nb + i] = ts + excl;
+      }
+      excl += tot[j];
+    }
+    if (s == 0 && t == T - 1 && threadIdx.x == 0) bucket_start[T * nb] = __ldg(offsets + T * B);
+  }
+  const int32_t bag_lo = static_cast<int32_t>(t * B), bag_hi = bag_lo + B;
+  const uint32_t key_hi = static_cast<uint32_t>(t) << idx_bits;
+
+  for (int32_t tile = a; tile < b; tile += kScatterTile) {
+    const int32_t tile_end = min(b, tile + kScatterTile);
+    for (int i = threadIdx.x; i < nb; i += kScatterThreads) cnt[i] = 0;
+    __syncthreads();  // also orders tstart, and the previous tile's use of stage / cnt / delta
+
+    // Every warp takes kRounds * 32 consecutive positions, which makes the bag of a position cheap:
+    // `cur` is a bag that starts at or before the warp's position, `ends` the ends of bags cur..cur+31.
+    const int32_t wa = tile + w * (32 * kRounds), wb = min(tile_end, wa + 32 * kRounds);
+    uint32_t key[kRounds], slot[kRounds];
+    int32_t bagv[kRounds];
+    if (wa < wb) {
+      int32_t cur = warp_find_bag(offsets, bag_lo, bag_hi, wa, lane);
+      int32_t ends = load_bag_ends(offsets, cur, bag_hi, lane);
+      int32_t index[kRounds];
+#pragma unroll
+      for (int r = 0; r < kRounds; ++r) index[r] = wa + r * 32 + lane < wb ? __ldg(indices + wa + r * 32 + lane) : 0;
+#pragma unroll
+      for (int r = 0; r < kRounds; ++r) {
+        const int32_t p = wa + r * 32 + lane;
+        const bool valid = p < wb;
+        // bag of p = cur + number of bag ends that are <= p
+        int32_t bag = -1, from = cur, window = ends;
+        while (true) {
+          const int c = count_not_above(window, p);
+          if (bag < 0 && valid && c < 32) bag = from + c;
+          if (__all_sync(0xffffffffu, bag >= 0 || !valid)) break;
+          from += 32;  // more than 32 bags end inside these 32 positions (short or empty bags)
+          window = load_bag_ends(offsets, from, bag_hi, lane);
+        }
+        const int32_t tail = __shfl_sync(0xffffffffu, bag, 31);
+        if (tail - cur >= 16) {  // slide the window before it runs out (tail is -1 past the share's end)
+          cur = tail;
+          ends = load_bag_ends(offsets, cur, bag_hi, lane);
+        }
+        key[r] = key_hi | static_cast<uint32_t>(index[r]);
+        bagv[r] = bag;
+        if (valid) {
+          const uint32_t bk = bucket_of(index[r], shift, nb);
+          slot[r] = bk | (static_cast<uint32_t>(atomicAdd(&cnt[bk], 1)) << 10);
+        }
+      }
+    }
+    __syncthreads();
+    {
+      int32_t c[kPer];
+      int32_t sum = 0;
+#pragma unroll
+      for (int j = 0; j < kPer; ++j) {
+        const int i = threadIdx.x * kPer + j;
+        c[j] = i < nb ? cnt[i] : 0;
+        sum += c[j];
+      }
+      int32_t excl;
+      Scan(scan_tmp).ExclusiveSum(sum, excl);
+#pragma unroll
+      for (int j = 0; j < kPer; ++j) {
+        const int i = threadIdx.x * kPer + j;
+        if (i < nb) {
+          cnt[i] = excl;
+          delta[i] = tstart[i] + (c[j] ? atomicAdd(reserved + t * nb + i, c[j]) : 0) - excl;
+        }
+        excl += c[j];
+      }
+    }
+    __syncthreads();
+    if (wa < wb) {
+#pragma unroll
+      for (int r = 0; r < kRounds; ++r)
+        if (wa + r * 32 + lane < wb)
+          stage[cnt[slot[r] & 1023u] + (slot[r] >> 10)] = make_uint2(key[r], static_cast<uint32_t>(bagv[r]));
+    }
+    __syncthreads();
+    const uint32_t index_mask = (1u << idx_bits) - 1u;
+    for (int i = threadIdx.x; i < tile_end - tile; i += kScatterThreads) {
+      const uint2 pr = stage[i];
+      pairs[delta[bucket_of(static_cast<int32_t>(pr.x & index_mask), shift, nb)] + i] = pr;
+    }
+  }
+}
+
+
+// Counter words are moved as 16-byte chunks; a thread scans 8 consecutive chunks at full size, so
+// chunk c lives at c ^ ((c >> 3) & 7): the 8 lanes of a quarter warp then hit 8 different bank groups.
+__device__ __forceinline__ int swizzle_chunk(int c) { return c ^ ((c >> 3) & 7); }
+__device__ __forceinline__ int swizzle_word(int i) { return (swizzle_chunk(i >> 2) << 2) | (i & 3); }
+
+// Dynamic shared memory: `words` counter words (two 16-bit counters each), then the bucket's keys and
+// values in counting-sort order.
+__global__ void __launch_bounds__(kRankThreads) bucket_rank_kernel(
+    const int32_t* __restrict__ bucket_start, const uint2* __restrict__ pairs, uint32_t* __restrict__ kout,
+    int32_t* __restrict__ vout, int bits, int words, int32_t* __restrict__ queue_count, int2* __restrict__ queue,
+    int queue_cap) {
+  extern __shared__ uint4 smem4[];
+  uint32_t* cnt = reinterpret_cast<uint32_t*>(smem4);
+  uint32_t* sk = cnt + words;
+  int32_t* sv = reinterpret_cast<int32_t*>(sk + kBucketSortCapacity);
+  using Scan = cub::BlockScan<uint32_t, kRankThreads>;
+  __shared__ typename Scan::TempStorage scan_tmp;
+
+  const int32_t start = __ldg(bucket_start + blockIdx.x), end = __ldg(bucket_start + blockIdx.x + 1);
+  const int32_t n = end - start;
+  if (n <= 0) return;
+  if (n > kBucketSortCapacity) {
+    if (threadIdx.x == 0) {
+      const int q = atomicAdd(queue_count, 1);
+      if (q < queue_cap) queue[q] = make_int2(start, end);  // always true: fewer than N / capacity such buckets
+    }
+    return;
+  }
+  pairs += start;
+  kout += start;
+  vout += start;
+  const uint32_t low_mask = (1u << bits) - 1u;
+  const int chunks = words >> 2;
+  const int cpt = (chunks + kRankThreads - 1) / kRankThreads;  // chunks a thread zeroes and scans
+  const int c0 = threadIdx.x * cpt;
+  for (int c = c0; c < min(c0 + cpt, chunks); ++c) smem4[swizzle_chunk(c)] = make_uint4(0u, 0u, 0u, 0u);
+  __syncthreads();
+
+  // count: the old value of a pair's counter is its arrival number among the pairs of its row
+  uint32_t key[kRankItems], where[kRankItems];
+  int32_t val[kRankItems];
+#pragma unroll
+  for (int j = 0; j < kRankItems; ++j) {
+    const int e = threadIdx.x + j * kRankThreads;
+    if (e < n) {
+      const uint2 pr = __ldg(pairs + e);
+      key[j] = pr.x;
+      val[j] = static_cast<int32_t>(pr.y);
+      const uint32_t low = pr.x & low_mask;
+      const int half = (low & 1u) * 16;
+      where[j] = (atomicAdd(&cnt[swizzle_word(low >> 1)], 1u << half) >> half) & 0xffffu;
+    }
+  }
+  __syncthreads();
+
+  // counts -> first position of every row, in place (positions fit 16 bits)
+  {
+    uint32_t packed = 0;
+    for (int c = c0; c < min(c0 + cpt, chunks); ++c) {
+      const uint4 v = smem4[swizzle_chunk(c)];
+      packed += v.x + v.y + v.z + v.w;  // both halves at once: neither can overflow 16 bits
+    }
+    uint32_t run;
+    Scan(scan_tmp).ExclusiveSum((packed & 0xffffu) + (packed >> 16), run);
+    for (int c = c0; c < min(c0 + cpt, chunks); ++c) {
+      uint4 v = smem4[swizzle_chunk(c)];
+      uint32_t* wv = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t lo = wv[i] & 0xffffu, hi = wv[i] >> 16;
+        const uint32_t second = run + lo;
+        wv[i] = run | (second << 16);
+        run = second + hi;
+      }
+      smem4[swizzle_chunk(c)] = v;
+    }
+  }
+  __syncthreads();
+
+  // place in counting-sort order; where = position | first position of the row << 16
+#pragma unroll
+  for (int j = 0; j < kRankItems; ++j) {
+    const int e = threadIdx.x + j * kRankThreads;
+    if (e < n) {
+      const uint32_t low = key[j] & low_mask;
+      const uint32_t first = (cnt[swizzle_word(low >> 1)] >> ((low & 1u) * 16)) & 0xffffu;
+      const uint32_t pos = first + where[j];
+      sk[pos] = key[j];
+      sv[pos] = val[j];
+      where[j] = pos | (first << 16);
+    }
+  }
+  __syncthreads();
+
+  // Pairs that share a counter (normally: the same row) are ordered by (key, bag id); among equal
+  // pairs the arrival order stands, which cannot be told apart in the output.  where = final
+  // position of a pair that has to move, else all ones.
+#pragma unroll
+  for (int j = 0; j < kRankItems; ++j) {
+    const int e = threadIdx.x + j * kRankThreads;
+    if (e < n) {
+      const int pos = where[j] & 0xffffu, first = where[j] >> 16;
+      const uint32_t low = key[j] & low_mask;
+      where[j] = 0xffffffffu;
+      if (pos > first || (pos + 1 < n && (sk[pos + 1] & low_mask) == low)) {
+        int rank = 0;
+        for (int q = first; q < n; ++q) {
+          const uint32_t kq = sk[q];
+          if ((kq & low_mask) != low) break;
+          const int32_t vq = sv[q];
+          rank += (kq < key[j]) || (kq == key[j] && (vq < val[j] || (vq == val[j] && q < pos)));
+        }
+        if (first + rank != pos) where[j] = static_cast<uint32_t>(first + rank);
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < kRankItems; ++j) {
+    if (threadIdx.x + j * kRankThreads < n && where[j] != 0xffffffffu) {
+      sk[where[j]] = key[j];
+      sv[where[j]] = val[j];
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += kRankThreads) {
+    kout[i] = sk[i];
+    vout[i] = sv[i];
+  }
+}
+
+
+// One stable radix pass of a CTA of W warps over n pairs, on bits [sh, sh + dbits) of the key or,
+// with BY_VAL, of value - vbase.  Every warp owns a contiguous share of the input, counts its
+// digits, the counts become start positions in (digit, warp) order, then the warp walks its share 32
+// pairs at a time and ranks equal digits with ballots.  cnt: W * kMaxDigits counters, digit_base:
+// kMaxDigits.
+template <int W, bool BY_VAL>
+__device__ __forceinline__ void radix_pass(const uint32_t* sk, const int32_t* sv, uint32_t* dk, int32_t* dv, int32_t n,
+                                           int32_t vbase, int sh, int dbits, int32_t* cnt, int32_t* digit_base) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int nd = 1 << dbits;
+  const uint32_t mask = static_cast<uint32_t>(nd - 1);
+  int32_t ca, cb;
+  warp_share(0, n, w, W, &ca, &cb);
+  int32_t* my_cnt = cnt + w * kMaxDigits;
+  for (int i = lane; i < nd; i += 32) my_cnt[i] = 0;
+  __syncwarp();
+  for (int32_t p = ca + lane; p < cb; p += 32) {
+    const uint32_t x = BY_VAL ? static_cast<uint32_t>(sv[p] - vbase) : sk[p];
+    atomicAdd(&my_cnt[(x >> sh) & mask], 1);
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < nd; d += W * 32) {
+    int32_t run = 0;
+#pragma unroll 8
+    for (int w2 = 0; w2 < W; ++w2) {
+      const int32_t c = cnt[w2 * kMaxDigits + d];
+      cnt[w2 * kMaxDigits + d] = run;
+      run += c;
+    }
+    digit_base[d] = run;
+  }
+  __syncthreads();
+  if (w == 0) {  // exclusive scan of the per-digit totals
+    constexpr int kPer = kMaxDigits / 32;
+    int32_t v[kPer];
+    int32_t sum = 0;
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int d = lane * kPer + j;
+      v[j] = d < nd ? digit_base[d] : 0;
+      sum += v[j];
+    }
+    int32_t incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    int32_t run = incl - sum;
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int d = lane * kPer + j;
+      if (d < nd) digit_base[d] = run;
+      run += v[j];
+    }
+  }
+  __syncthreads();
+  for (int32_t p0 = ca; p0 < cb; p0 += 32) {
+    const int32_t p = p0 + lane;
+    const bool valid = p < cb;
+    const uint32_t key = valid ? sk[p] : 0u;
+    const int32_t val = valid ? sv[p] : vbase;
+    const uint32_t d = ((BY_VAL ? static_cast<uint32_t>(val - vbase) : key) >> sh) & mask;
+    uint32_t peers = __ballot_sync(0xffffffffu, valid);
+    for (int bit = 0; bit < dbits; ++bit) {
+      const bool one = (d >> bit) & 1u;
+      const uint32_t set = __ballot_sync(0xffffffffu, one);
+      peers &= one ? set : ~set;
+    }
+    const int r = __popc(peers & ((1u << lane) - 1u));
+    if (valid) {
+      const int32_t pos = digit_base[d] + my_cnt[d] + r;
+      dk[pos] = key;
+      dv[pos] = val;
+    }
+    __syncwarp();
+    if (valid && r == 0) my_cnt[d] += __popc(peers);
+    __syncwarp();
+  }
+  __syncthreads();
+}
+
+// Buckets too large for bucket_rank_kernel: least-significant-digit radix sort on (index bits, bag
+// id within the table).  The bucket's pairs are first split into the output arrays; the passes then
+// ping-pong between those and the bucket's own stretch of the pair array, which is free by then.  A
+// fixed grid walks the queue, so an empty queue costs one launch.
+__global__ void __launch_bounds__(kOversizeThreads) oversize_sort_kernel(uint2* pairs, uint32_t* kout, int32_t* vout,
+                                                                         int key_bits, int bag_bits, int idx_bits,
+                                                                         int32_t B,
+                                                                         const int32_t* __restrict__ queue_count,
+                                                                         const int2* __restrict__ queue,
+                                                                         int queue_cap) {
+  __shared__ int32_t cnt[kOversizeWarps * kMaxDigits];
+  __shared__ int32_t digit_base[kMaxDigits];
+  const int count = min(*queue_count, queue_cap);
+  const int vp = (bag_bits + 7) / 8, kp = (key_bits + 7) / 8;
+  const int vd = vp ? (bag_bits + vp - 1) / vp : 0, kd = kp ? (key_bits + kp - 1) / kp : 0;
+  for (int q = blockIdx.x; q < count; q += gridDim.x) {
+    const int2 seg = queue[q];
+    const int32_t n = seg.y - seg.x;
+    uint32_t* scratch = reinterpret_cast<uint32_t*>(pairs + seg.x);
+    uint32_t* k[2] = {kout + seg.x, scratch};
+    int32_t* v[2] = {vout + seg.x, reinterpret_cast<int32_t*>(scratch + n)};
+    const int32_t vbase = static_cast<int32_t>(pairs[seg.x].x >> idx_bits) * B;  // first bag of the bucket's table
+    for (int32_t i = threadIdx.x; i < n; i += kOversizeThreads) {
+      const uint2 pr = pairs[seg.x + i];
+      k[0][i] = pr.x;
+      v[0][i] = static_cast<int32_t>(pr.y);
+    }
+    __syncthreads();
+    int side = 0;
+    for (int pass = 0; pass < vp; ++pass, side ^= 1)
+      radix_pass<kOversizeWarps, true>(k[side], v[side], k[side ^ 1], v[side ^ 1], n, vbase, pass * vd,
+                                       min(vd, bag_bits - pass * vd), cnt, digit_base);
+    for (int pass = 0; pass < kp; ++pass, side ^= 1)
+      radix_pass<kOversizeWarps, false>(k[side], v[side], k[side ^ 1], v[side ^ 1], n, vbase, pass * kd,
+                                        min(kd, key_bits - pass * kd), cnt, digit_base);
+    if (side == 1) {  // an odd number of passes ends in the scratch
+      for (int32_t i = threadIdx.x; i < n; i += kOversizeThreads) {
+        k[0][i] = k[1][i];
+        v[0][i] = v[1][i];
+      }
+      __syncthreads();
+    }
+  }
+}
+
+int rank_words(int bits) {
+  const int w = (1 << bits) / 2;
+  return w < 32 ? 32 : w;  // whole swizzle groups of 8 chunks
+}
+
+}  // namespace
+
+bool bucket_geometry(int64_t T, int64_t N, int64_t max_rows_per_table, KeyLayout layout, const Workspace& ws,
+                     BucketGeometry* g) {
+  if (layout.idx_bits == 0 || N < 1 || max_rows_per_table < 1) return false;
+  if (tuning(kTuneBwdSort) == 1) return false;
+  const double avg = static_cast<double>(N) / static_cast<double>(T);
+  double target = tuning(kTuneSortBucket);
+  if (target <= 0) target = kDefaultBucketTarget;
+  if (target > kBucketSortCapacity * 0.7) target = kBucketSortCapacity * 0.7;
+  // widest bucket (fewest buckets) whose expected size under uniform indices stays below the target
+  int shift = layout.idx_bits < kRankBits ? layout.idx_bits : kRankBits;
+  while (shift > 0 && avg * static_cast<double>(1ll << shift) / static_cast<double>(max_rows_per_table) > target)
+    --shift;
+  const int64_t nb = ((max_rows_per_table - 1) >> shift) + 1;
+  if (nb > kMaxBuckets) return false;  // tables too large (or too busy) for 1024 buckets of 2^14 rows
+  g->shift = shift;
+  g->nb = static_cast<int>(nb);
+  const int64_t want = static_cast<int64_t>(avg / 8192.0) + 1;
+  const int64_t room = 3ll * device_sm_count() / T;  // the (slice, table) grid should be resident at once
+  int64_t S = want < room ? want : room;
+  if (S < 1) S = 1;
+  if (S > 65535 || T > 65535) return false;
+  g->slices = static_cast<int>(S);
+  if (2 * T * nb > ws.hist_cap || T * nb + 1 > ws.hist_cap) return false;
+  return true;
+}
+
+int bucket_sort_plan(const int32_t* indices, const int32_t* offsets, int64_t T, int64_t B, int64_t N,
+                     KeyLayout layout, const BucketGeometry& g, Workspace& ws, cudaStream_t stream) {
+  const dim3 grid(static_cast<unsigned>(g.slices), static_cast<unsigned>(T));
+  const int qcap = static_cast<int>(ws.queue_cap);
+  int32_t* queue_count = ws.counters + 8;
+  int32_t* totals = ws.hist;
+  int32_t* reserved = ws.hist + T * g.nb;
+  // (key, bag id) pairs between the two levels; keys_in and vals_in are adjacent in the workspace
+  uint2* pairs = reinterpret_cast<uint2*>(ws.keys_in);
+  const int words = rank_words(g.shift);
+  const size_t rank_smem = static_cast<size_t>(words) * 4 + static_cast<size_t>(kBucketSortCapacity) * 8;
+  int dev = 0;
+  TBE_CUDA_TRY(cudaGetDevice(&dev));
+  static std::atomic<bool> opted_in[64];
+  if (dev < 64 && !opted_in[dev].load(std::memory_order_acquire)) {
+    TBE_CUDA_TRY(cudaFuncSetAttribute(bucket_rank_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kRankWords * 4 + kBucketSortCapacity * 8));
+    opted_in[dev].store(true, std::memory_order_release);
+  }
+  TBE_CUDA_TRY(cudaMemsetAsync(totals, 0, static_cast<size_t>(2 * T * g.nb) * 4, stream));
+  TBE_CUDA_TRY(cudaMemsetAsync(queue_count, 0, 4, stream));
+  {
+    KernelTimer timer("bucket_count_kernel", stream);
+    bucket_count_kernel<<<grid, kCountThreads, 0, stream>>>(indices, offsets, static_cast<int32_t>(B), g.shift, g.nb,
+                                                            totals);
+  }
+  TBE_CHECK_LAUNCH("bucket_count_kernel");
+  {
+    KernelTimer timer("bucket_scatter_kernel", stream);
+    bucket_scatter_kernel<<<grid, kScatterThreads, 0, stream>>>(indices, offsets, static_cast<int32_t>(B), T,
+                                                                layout.idx_bits, g.shift, g.nb, totals, reserved,
+                                                                ws.bucket_start, pairs);
+  }
+  TBE_CHECK_LAUNCH("bucket_scatter_kernel");
+  {
+    KernelTimer timer("bucket_rank_kernel", stream);
+    bucket_rank_kernel<<<static_cast<unsigned>(T * g.nb), kRankThreads, rank_smem, stream>>>(
+        ws.bucket_start, pairs, ws.keys, ws.vals, g.shift, words, queue_count, ws.oversize, qcap);
+  }
+  TBE_CHECK_LAUNCH("bucket_rank_kernel");
+  {
+    int blocks = 2 * device_sm_count();
+    if (blocks > qcap) blocks = qcap;
+    int bag_bits = 0;
+    while ((1ll << bag_bits) < B) ++bag_bits;
+    KernelTimer timer("oversize_sort_kernel", stream);
+    oversize_sort_kernel<<<static_cast<unsigned>(blocks), kOversizeThreads, 0, stream>>>(
+        pairs, ws.keys, ws.vals, g.shift, bag_bits, layout.idx_bits, static_cast<int32_t>(B), queue_count,
+        ws.oversize, qcap);
+  }
+  TBE_CHECK_LAUNCH("oversize_sort_kernel");
+  return TBE_OK;
+}
+
+}  // namespace tbe

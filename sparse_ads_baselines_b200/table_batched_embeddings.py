@@ -415,9 +415,11 @@ def backward_exact_adagrad_mixed_D(grad_output, weights, table_offsets, table_di
                            indices, offsets, None, optimizer_state, learning_rate, eps, stochastic_rounding)
 
 
-def sort_segments(table_offsets, indices, offsets, total_rows):
+def sort_segments(table_offsets, indices, offsets, total_rows, max_rows_per_table=0):
     """The backward's integer bookkeeping: ``(sorted_rows, sorted_bags, segment_starts)`` with
-    ``segment_starts`` trimmed to the number of distinct rows (synchronises to read that count)."""
+    ``segment_starts`` trimmed to the number of distinct rows (synchronises to read that count).
+    ``max_rows_per_table`` > 0 (an upper bound on every table's row count, tables laid out in
+    ascending order) selects the table-segmented sort the optimizer calls use."""
     _check_cuda("table_offsets", table_offsets, torch.int32)
     _check_cuda("indices", indices, torch.int32)
     _check_cuda("offsets", offsets, torch.int32)
@@ -435,7 +437,8 @@ def sort_segments(table_offsets, indices, offsets, total_rows):
             raise _lib.TBEError("tbe_backward_workspace_bytes", nbytes, _lib.last_error())
         ws = _workspace(dev, nbytes)
         _lib.call("tbe_sort_segments", table_offsets.data_ptr(), indices.data_ptr(), offsets.data_ptr(),
-                  T, B, N, total_rows, rows.data_ptr(), bags.data_ptr(), starts.data_ptr(), count.data_ptr(),
+                  T, B, N, total_rows, int(max_rows_per_table), rows.data_ptr(), bags.data_ptr(), starts.data_ptr(),
+                  count.data_ptr(),
                   ws.data_ptr(), ws.numel(), _stream(dev))
         u = int(count.item())
     return rows[:N], bags[:N], starts[:u]

@@ -52,6 +52,86 @@ def test_sort_segments_empty_input(cuda_device):
     assert rows.numel() == 0 and bags.numel() == 0 and starts.numel() == 0
 
 
+def _table_sort_case(rng, T, E, B, Lmax, hot):
+    """Ragged bags (empty ones included); with ``hot`` most lookups of a table hit a few rows, so one
+    bucket of the table-segmented sort outgrows a CTA and takes the queued path."""
+    lengths = rng.integers(0, Lmax + 1, size=(T, B))
+    lengths[rng.random((T, B)) < 0.1] = 0
+    offsets = oracle.offsets_from_lengths(lengths)
+    N = int(offsets[-1])
+    indices = rng.integers(0, E, size=N).astype(np.int32)
+    if hot:
+        pick = rng.random(N) < 0.8
+        indices[pick] = rng.integers(0, min(E, 3), size=int(pick.sum())).astype(np.int32)
+    return indices, offsets.astype(np.int32)
+
+
+@pytest.mark.parametrize("T,E,B,Lmax,hot", [
+    (1, 1, 1, 1, False),
+    (3, 17, 5, 6, False),              # a bucket is one row: nothing to sort inside it
+    (2, 1000, 4096, 16, False),        # several slices and tiles per table
+    (2, 1000, 4096, 16, True),         # oversize buckets
+    (5, 70000, 2048, 40, False),       # many buckets per table, rows not a power of two
+    (5, 70000, 2048, 40, True),
+    (70, 300000, 64, 30, False),       # more tables than one slice each can fill
+    (1, 2 ** 20, 3000, 50, False),
+    (3, 2 ** 20 + 1, 1500, 50, True),  # index bits roll over to 21
+])
+def test_table_segmented_sort_exact(cuda_device, T, E, B, Lmax, hot):
+    """With max_rows_per_table the plan comes from the table-segmented two-level sort; rows, bags and
+    run starts must equal the oracle's stable sort exactly, and the device radix sort's."""
+    rng = np.random.default_rng(T * 1000 + B + int(hot))
+    indices, offsets = _table_sort_case(rng, T, E, B, Lmax, hot)
+    dev = cuda_device
+    to_np = np.arange(T, dtype=np.int64) * E
+    to = torch.from_numpy(to_np.astype(np.int32)).to(dev)
+    idx, off = torch.from_numpy(indices).to(dev), torch.from_numpy(offsets).to(dev)
+    r0, b0, s0 = oracle.sort_segments(list(to_np), indices, offsets)
+    for sort_mode in (0, 1):
+        _lib.call("tbe_set_tuning", b"bwd_sort", sort_mode)
+        try:
+            rows, bags, starts = tbe.sort_segments(to, idx, off, T * E, max_rows_per_table=E)
+        finally:
+            _lib.call("tbe_set_tuning", b"bwd_sort", 0)
+        assert np.array_equal(rows.cpu().numpy(), r0), sort_mode
+        assert np.array_equal(bags.cpu().numpy(), b0), sort_mode
+        assert np.array_equal(starts.cpu().numpy(), s0), sort_mode
+
+
+@pytest.mark.parametrize("bucket", [64, 300, 2048])
+def test_table_segmented_sort_bucket_sizes(cuda_device, bucket):
+    """The bucket-size knob changes the geometry (buckets per table, CTA variants), never the result."""
+    rng = np.random.default_rng(bucket)
+    T, E, B = 4, 50000, 1024
+    indices, offsets = _table_sort_case(rng, T, E, B, 24, False)
+    dev = cuda_device
+    to_np = np.arange(T, dtype=np.int64) * E
+    to = torch.from_numpy(to_np.astype(np.int32)).to(dev)
+    idx, off = torch.from_numpy(indices).to(dev), torch.from_numpy(offsets).to(dev)
+    r0, b0, s0 = oracle.sort_segments(list(to_np), indices, offsets)
+    _lib.call("tbe_set_tuning", b"sort_bucket", bucket)
+    try:
+        rows, bags, starts = tbe.sort_segments(to, idx, off, T * E, max_rows_per_table=E)
+    finally:
+        _lib.call("tbe_set_tuning", b"sort_bucket", 0)
+    assert np.array_equal(rows.cpu().numpy(), r0)
+    assert np.array_equal(bags.cpu().numpy(), b0)
+    assert np.array_equal(starts.cpu().numpy(), s0)
+
+
+def test_sgd_same_bits_with_either_sort(cuda_device):
+    """The two plans order every run identically, so the updated weights agree bit for bit."""
+    c = to_device(make_case(T=6, E=3000, D=64, B=512, Lmax=30, dtype=torch.float16, seed=11), cuda_device)
+    out = []
+    for sort_mode in (0, 1):
+        _lib.call("tbe_set_tuning", b"bwd_sort", sort_mode)
+        try:
+            out.append(_sgd(c, 0.05))
+        finally:
+            _lib.call("tbe_set_tuning", b"bwd_sort", 0)
+    assert torch.equal(out[0], out[1])
+
+
 @pytest.mark.parametrize("D", [4, 8, 12, 64, 100, 128, 256, 260, 2048])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
 @pytest.mark.parametrize("pooling", ["sum", "mean"])
