@@ -25,8 +25,6 @@
 //                              through global memory, first on the bag id, then on the index bits.
 //                              Skewed batches, where a few hot rows put most of a table in one
 //                              bucket, land here; normally the queue is empty.
-#include <cub/block/block_scan.cuh>
-
 #include <atomic>
 
 #include "tbe_plan.cuh"
@@ -72,22 +70,52 @@ __device__ __forceinline__ void warp_share(int32_t a, int32_t b, int w, int W, i
   *cb = lo + per < b ? static_cast<int32_t>(lo + per) : b;
 }
 
-// totals[t * nb + bucket] += lookups of slice s of table t that fall in the bucket (zeroed by the host).
+// Exclusive prefix sum of x over the threads of a CTA: shuffles inside a warp, then the totals of the
+// warps in front.  Warps flagged inactive hold zeros and skip the work; every thread must call it,
+// and a barrier must separate two calls that share warp_tot (one entry per warp).
+template <typename V>
+__device__ __forceinline__ V cta_exclusive_scan(V x, V* warp_tot, bool warp_active) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  V incl = x;
+  if (warp_active) {
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const V up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+  }
+  if (lane == 31) warp_tot[w] = warp_active ? incl : V(0);
+  __syncthreads();
+  V base = 0;
+  if (warp_active)
+    for (int i = 0; i < w; ++i) base += warp_tot[i];
+  return base + incl - x;
+}
+
+// hist[(t * S + s) * nb + bucket] = lookups of slice s of table t that fall in the bucket.
 __global__ void __launch_bounds__(kCountThreads) bucket_count_kernel(const int32_t* __restrict__ indices,
                                                                      const int32_t* __restrict__ offsets, int32_t B,
-                                                                     int shift, int nb, int32_t* __restrict__ totals) {
+                                                                     int shift, int nb, int32_t* __restrict__ hist,
+                                                                     int32_t* __restrict__ queue_count) {
   __shared__ int32_t sh[kMaxBuckets];
   const int s = blockIdx.x, S = gridDim.x;
   const int64_t t = blockIdx.y;
   for (int i = threadIdx.x; i < nb; i += kCountThreads) sh[i] = 0;
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *queue_count = 0;  // no oversize buckets yet
   __syncthreads();
   int32_t ts, a, b;
   slice_range(offsets, t, B, s, S, &ts, &a, &b);
-  for (int32_t p = a + threadIdx.x; p < b; p += kCountThreads)
-    atomicAdd(&sh[bucket_of(__ldg(indices + p), shift, nb)], 1);
+  for (int32_t p = a + threadIdx.x; p < b; p += 4 * kCountThreads) {
+    int32_t index[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) index[j] = p + j * kCountThreads < b ? __ldg(indices + p + j * kCountThreads) : -1;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (p + j * kCountThreads < b) atomicAdd(&sh[bucket_of(index[j], shift, nb)], 1);
+  }
   __syncthreads();
-  for (int i = threadIdx.x; i < nb; i += kCountThreads)
-    if (sh[i]) atomicAdd(totals + t * nb + i, sh[i]);
+  int32_t* out = hist + (t * S + s) * nb;
+  for (int i = threadIdx.x; i < nb; i += kCountThreads) out[i] = sh[i];
 }
 
 // Largest bag g in [lo, hi) with offsets[g] <= p (offsets[lo] <= p is given).  All lanes call it with
@@ -125,45 +153,58 @@ __device__ __forceinline__ int count_not_above(int32_t ends, int32_t p) {
   return c;
 }
 
-// A CTA walks its slice in tiles of kScatterTile positions.  Per tile: count the buckets (the old
-// value of a pair's counter is its slot among the tile's pairs of that bucket), reserve room for the
-// tile in every bucket with one global atomic per bucket, gather the pairs bucket by bucket in shared
-// memory, then copy them out: a bucket's share of the tile is one contiguous run of 8-byte pairs, so
-// the stores coalesce instead of costing a sector per pair.
+// A CTA moves its slice in steps of kScatterTile pairs.  Every warp owns a contiguous share of the
+// slice and contributes its next 32 * kRounds positions to each step (walking one contiguous range
+// keeps the search for the bag of a position a matter of a few shuffles).  Per step: count the
+// buckets (the old value of a pair's counter is its slot among the step's pairs of that bucket),
+// gather the pairs bucket by bucket in shared memory, then copy them out: a bucket's share of the
+// step is one contiguous run of 8-byte pairs, so the stores coalesce instead of costing a sector per
+// pair.  Where a slice's pairs go inside a bucket follows from the histograms alone: slices in order.
 __global__ void __launch_bounds__(kScatterThreads, 3) bucket_scatter_kernel(
     const int32_t* __restrict__ indices, const int32_t* __restrict__ offsets, int32_t B, int64_t T, int idx_bits,
-    int shift, int nb, const int32_t* __restrict__ totals, int32_t* __restrict__ reserved,
-    int32_t* __restrict__ bucket_start, uint2* __restrict__ pairs) {
+    int shift, int nb, const int32_t* __restrict__ hist, int32_t* __restrict__ bucket_start,
+    uint2* __restrict__ pairs) {
   __shared__ uint2 stage[kScatterTile];
-  __shared__ int32_t cnt[kMaxBuckets];     // pairs of the tile per bucket, then their first slot in `stage`
+  __shared__ int32_t cnt[kMaxBuckets];     // pairs of the step per bucket, then their first slot in `stage`
   __shared__ int32_t delta[kMaxBuckets];   // global position minus slot in `stage`, per bucket
-  __shared__ int32_t tstart[kMaxBuckets];  // first position of every bucket of the table
-  using Scan = cub::BlockScan<int32_t, kScatterThreads>;
-  __shared__ typename Scan::TempStorage scan_tmp;
+  __shared__ int32_t cursor[kMaxBuckets];  // next free global position of this slice in every bucket
+  __shared__ int32_t warp_tot[kScatterThreads / 32];
+  __shared__ int32_t step_total;
   constexpr int kPer = kMaxBuckets / kScatterThreads;  // buckets per thread
   constexpr int kRounds = kScatterTile / kScatterThreads;
+  constexpr int kWarps = kScatterThreads / 32;
 
   const int s = blockIdx.x, S = gridDim.x;
   const int64_t t = blockIdx.y;
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   int32_t ts, a, b;
   slice_range(offsets, t, B, s, S, &ts, &a, &b);
+  const bool scans = w * 32 * kPer < nb;  // this warp's threads own buckets
   {
-    int32_t tot[kPer];
+    int32_t tot[kPer], before[kPer];
     int32_t sum = 0;
+    const int32_t* h = hist + t * S * nb;
 #pragma unroll
     for (int j = 0; j < kPer; ++j) {
       const int i = threadIdx.x * kPer + j;
-      tot[j] = i < nb ? __ldg(totals + t * nb + i) : 0;
+      tot[j] = 0;
+      before[j] = 0;
+      if (i < nb) {
+        for (int s2 = 0; s2 < S; ++s2) {
+          const int32_t c = __ldg(h + s2 * nb + i);
+          if (s2 < s) before[j] += c;
+          tot[j] += c;
+        }
+      }
       sum += tot[j];
     }
-    int32_t excl;
-    Scan(scan_tmp).ExclusiveSum(sum, excl);
+    int32_t excl = cta_exclusive_scan(sum, warp_tot, scans);
 #pragma unroll
     for (int j = 0; j < kPer; ++j) {
       const int i = threadIdx.x * kPer + j;
       if (i < nb) {
-        tstart[i] = ts + excl;
+        cursor[i] = ts + excl + before[j];
+        cnt[i] = 0;
         if (s == 0) bucket_start[t * nb + i] = ts + excl;
       }
       excl += tot[j];
@@ -172,27 +213,43 @@ __global__ void __launch_bounds__(kScatterThreads, 3) bucket_scatter_kernel(
   }
   const int32_t bag_lo = static_cast<int32_t>(t * B), bag_hi = bag_lo + B;
   const uint32_t key_hi = static_cast<uint32_t>(t) << idx_bits;
+  const uint32_t index_mask = (1u << idx_bits) - 1u;
+  int32_t ca, cb;
+  warp_share(a, b, w, kWarps, &ca, &cb);
+  const int32_t share = ((((b - a) + kWarps - 1) / kWarps) + 31) & ~31;  // as in warp_share
+  const int steps = (share + 32 * kRounds - 1) / (32 * kRounds);
+  // `cur` is a bag that starts at or before the warp's position, `ends` the ends of bags cur..cur+31
+  int32_t cur = bag_lo, ends = 0;
+  if (ca < cb) {
+    cur = warp_find_bag(offsets, bag_lo, bag_hi, ca, lane);
+    ends = load_bag_ends(offsets, cur, bag_hi, lane);
+  }
+  int32_t index[kRounds];
+#pragma unroll
+  for (int r = 0; r < kRounds; ++r) index[r] = ca + r * 32 + lane < cb ? __ldg(indices + ca + r * 32 + lane) : 0;
+  __syncthreads();
 
-  for (int32_t tile = a; tile < b; tile += kScatterTile) {
-    const int32_t tile_end = min(b, tile + kScatterTile);
-    for (int i = threadIdx.x; i < nb; i += kScatterThreads) cnt[i] = 0;
-    __syncthreads();  // also orders tstart, and the previous tile's use of stage / cnt / delta
-
-    // Every warp takes kRounds * 32 consecutive positions, which makes the bag of a position cheap:
-    // `cur` is a bag that starts at or before the warp's position, `ends` the ends of bags cur..cur+31.
-    const int32_t wa = tile + w * (32 * kRounds), wb = min(tile_end, wa + 32 * kRounds);
+  for (int k = 0; k < steps; ++k) {
+    const int32_t wa = min(cb, ca + k * (32 * kRounds));
     uint32_t key[kRounds], slot[kRounds];
     int32_t bagv[kRounds];
-    if (wa < wb) {
-      int32_t cur = warp_find_bag(offsets, bag_lo, bag_hi, wa, lane);
-      int32_t ends = load_bag_ends(offsets, cur, bag_hi, lane);
-      int32_t index[kRounds];
 #pragma unroll
-      for (int r = 0; r < kRounds; ++r) index[r] = wa + r * 32 + lane < wb ? __ldg(indices + wa + r * 32 + lane) : 0;
+    for (int r = 0; r < kRounds; ++r) {
+      const int32_t p = wa + r * 32 + lane;
+      const bool valid = p < cb;
+      key[r] = key_hi | static_cast<uint32_t>(index[r]);
+      if (valid) {
+        const uint32_t bk = bucket_of(index[r], shift, nb);
+        slot[r] = bk | (static_cast<uint32_t>(atomicAdd(&cnt[bk], 1)) << 10);
+      }
+      const int32_t pn = p + 32 * kRounds;  // the next step's index, in flight during this one
+      index[r] = pn < cb ? __ldg(indices + pn) : 0;
+    }
+    if (wa < cb) {
 #pragma unroll
       for (int r = 0; r < kRounds; ++r) {
         const int32_t p = wa + r * 32 + lane;
-        const bool valid = p < wb;
+        const bool valid = p < cb;
         // bag of p = cur + number of bag ends that are <= p
         int32_t bag = -1, from = cur, window = ends;
         while (true) {
@@ -207,12 +264,7 @@ __global__ void __launch_bounds__(kScatterThreads, 3) bucket_scatter_kernel(
           cur = tail;
           ends = load_bag_ends(offsets, cur, bag_hi, lane);
         }
-        key[r] = key_hi | static_cast<uint32_t>(index[r]);
         bagv[r] = bag;
-        if (valid) {
-          const uint32_t bk = bucket_of(index[r], shift, nb);
-          slot[r] = bk | (static_cast<uint32_t>(atomicAdd(&cnt[bk], 1)) << 10);
-        }
       }
     }
     __syncthreads();
@@ -225,52 +277,54 @@ __global__ void __launch_bounds__(kScatterThreads, 3) bucket_scatter_kernel(
         c[j] = i < nb ? cnt[i] : 0;
         sum += c[j];
       }
-      int32_t excl;
-      Scan(scan_tmp).ExclusiveSum(sum, excl);
+      int32_t excl = cta_exclusive_scan(sum, warp_tot, scans);
 #pragma unroll
       for (int j = 0; j < kPer; ++j) {
         const int i = threadIdx.x * kPer + j;
         if (i < nb) {
           cnt[i] = excl;
-          delta[i] = tstart[i] + (c[j] ? atomicAdd(reserved + t * nb + i, c[j]) : 0) - excl;
+          delta[i] = cursor[i] - excl;
+          cursor[i] += c[j];
+          if (i == nb - 1) step_total = excl + c[j];
         }
         excl += c[j];
       }
     }
     __syncthreads();
-    if (wa < wb) {
 #pragma unroll
-      for (int r = 0; r < kRounds; ++r)
-        if (wa + r * 32 + lane < wb)
-          stage[cnt[slot[r] & 1023u] + (slot[r] >> 10)] = make_uint2(key[r], static_cast<uint32_t>(bagv[r]));
-    }
+    for (int r = 0; r < kRounds; ++r)
+      if (wa + r * 32 + lane < cb)
+        stage[cnt[slot[r] & 1023u] + (slot[r] >> 10)] = make_uint2(key[r], static_cast<uint32_t>(bagv[r]));
     __syncthreads();
-    const uint32_t index_mask = (1u << idx_bits) - 1u;
-    for (int i = threadIdx.x; i < tile_end - tile; i += kScatterThreads) {
+    for (int i = threadIdx.x; i < nb; i += kScatterThreads) cnt[i] = 0;
+    const int32_t m = step_total;
+    for (int i = threadIdx.x; i < m; i += kScatterThreads) {
       const uint2 pr = stage[i];
       pairs[delta[bucket_of(static_cast<int32_t>(pr.x & index_mask), shift, nb)] + i] = pr;
     }
+    __syncthreads();
   }
 }
-
 
 // Counter words are moved as 16-byte chunks; a thread scans 8 consecutive chunks at full size, so
 // chunk c lives at c ^ ((c >> 3) & 7): the 8 lanes of a quarter warp then hit 8 different bank groups.
 __device__ __forceinline__ int swizzle_chunk(int c) { return c ^ ((c >> 3) & 7); }
 __device__ __forceinline__ int swizzle_word(int i) { return (swizzle_chunk(i >> 2) << 2) | (i & 3); }
 
-// Dynamic shared memory: `words` counter words (two 16-bit counters each), then the bucket's keys and
+// Dynamic shared memory: a region that first holds `words` counter words (two 16-bit counters each)
+// and later the list of pairs that share their row with another pair, then the bucket's keys and
 // values in counting-sort order.
 __global__ void __launch_bounds__(kRankThreads) bucket_rank_kernel(
     const int32_t* __restrict__ bucket_start, const uint2* __restrict__ pairs, uint32_t* __restrict__ kout,
-    int32_t* __restrict__ vout, int bits, int words, int32_t* __restrict__ queue_count, int2* __restrict__ queue,
-    int queue_cap) {
+    int32_t* __restrict__ vout, int bits, int words, int region_words, int32_t* __restrict__ queue_count,
+    int2* __restrict__ queue, int queue_cap) {
   extern __shared__ uint4 smem4[];
   uint32_t* cnt = reinterpret_cast<uint32_t*>(smem4);
-  uint32_t* sk = cnt + words;
+  uint32_t* list = cnt;
+  uint32_t* sk = cnt + region_words;
   int32_t* sv = reinterpret_cast<int32_t*>(sk + kBucketSortCapacity);
-  using Scan = cub::BlockScan<uint32_t, kRankThreads>;
-  __shared__ typename Scan::TempStorage scan_tmp;
+  __shared__ uint32_t warp_tot[kRankThreads / 32];
+  __shared__ int list_n;
 
   const int32_t start = __ldg(bucket_start + blockIdx.x), end = __ldg(bucket_start + blockIdx.x + 1);
   const int32_t n = end - start;
@@ -285,24 +339,28 @@ __global__ void __launch_bounds__(kRankThreads) bucket_rank_kernel(
   pairs += start;
   kout += start;
   vout += start;
+  uint32_t key[kRankItems], where[kRankItems];
+  int32_t val[kRankItems];
+#pragma unroll
+  for (int j = 0; j < kRankItems; ++j) {  // in flight while the counters are cleared
+    const int e = threadIdx.x + j * kRankThreads;
+    const uint2 pr = e < n ? __ldg(pairs + e) : make_uint2(0u, 0u);
+    key[j] = pr.x;
+    val[j] = static_cast<int32_t>(pr.y);
+  }
   const uint32_t low_mask = (1u << bits) - 1u;
   const int chunks = words >> 2;
   const int cpt = (chunks + kRankThreads - 1) / kRankThreads;  // chunks a thread zeroes and scans
   const int c0 = threadIdx.x * cpt;
   for (int c = c0; c < min(c0 + cpt, chunks); ++c) smem4[swizzle_chunk(c)] = make_uint4(0u, 0u, 0u, 0u);
+  if (threadIdx.x == 0) list_n = 0;
   __syncthreads();
 
   // count: the old value of a pair's counter is its arrival number among the pairs of its row
-  uint32_t key[kRankItems], where[kRankItems];
-  int32_t val[kRankItems];
 #pragma unroll
   for (int j = 0; j < kRankItems; ++j) {
-    const int e = threadIdx.x + j * kRankThreads;
-    if (e < n) {
-      const uint2 pr = __ldg(pairs + e);
-      key[j] = pr.x;
-      val[j] = static_cast<int32_t>(pr.y);
-      const uint32_t low = pr.x & low_mask;
+    if (threadIdx.x + j * kRankThreads < n) {
+      const uint32_t low = key[j] & low_mask;
       const int half = (low & 1u) * 16;
       where[j] = (atomicAdd(&cnt[swizzle_word(low >> 1)], 1u << half) >> half) & 0xffffu;
     }
@@ -316,8 +374,7 @@ __global__ void __launch_bounds__(kRankThreads) bucket_rank_kernel(
       const uint4 v = smem4[swizzle_chunk(c)];
       packed += v.x + v.y + v.z + v.w;  // both halves at once: neither can overflow 16 bits
     }
-    uint32_t run;
-    Scan(scan_tmp).ExclusiveSum((packed & 0xffffu) + (packed >> 16), run);
+    uint32_t run = cta_exclusive_scan((packed & 0xffffu) + (packed >> 16), warp_tot, true);
     for (int c = c0; c < min(c0 + cpt, chunks); ++c) {
       uint4 v = smem4[swizzle_chunk(c)];
       uint32_t* wv = reinterpret_cast<uint32_t*>(&v);
@@ -333,58 +390,65 @@ __global__ void __launch_bounds__(kRankThreads) bucket_rank_kernel(
   }
   __syncthreads();
 
-  // place in counting-sort order; where = position | first position of the row << 16
+  // place in counting-sort order.  where = position | first position of the row << 16, top bit set
+  // when the row holds more than one pair (its next row starts more than one position later).
 #pragma unroll
   for (int j = 0; j < kRankItems; ++j) {
-    const int e = threadIdx.x + j * kRankThreads;
-    if (e < n) {
+    if (threadIdx.x + j * kRankThreads < n) {
       const uint32_t low = key[j] & low_mask;
-      const uint32_t first = (cnt[swizzle_word(low >> 1)] >> ((low & 1u) * 16)) & 0xffffu;
+      const int word = low >> 1;
+      const uint32_t packed = cnt[swizzle_word(word)];
+      uint32_t first, next;
+      if (low & 1u) {
+        first = packed >> 16;
+        next = word + 1 < words ? (cnt[swizzle_word(word + 1)] & 0xffffu) : static_cast<uint32_t>(n);
+      } else {
+        first = packed & 0xffffu;
+        next = packed >> 16;
+      }
+      if (low == low_mask) next = static_cast<uint32_t>(n);  // the last row of the bucket (bits may be 0)
       const uint32_t pos = first + where[j];
       sk[pos] = key[j];
       sv[pos] = val[j];
-      where[j] = pos | (first << 16);
+      where[j] = pos | (first << 16) | (next - first > 1u ? 0x80000000u : 0u);
     }
   }
   __syncthreads();
 
-  // Pairs that share a counter (normally: the same row) are ordered by (key, bag id); among equal
-  // pairs the arrival order stands, which cannot be told apart in the output.  where = final
-  // position of a pair that has to move, else all ones.
+  // Copy out; rows with several pairs still need those ordered, so list their pairs (the counters are
+  // dead by now).
 #pragma unroll
-  for (int j = 0; j < kRankItems; ++j) {
-    const int e = threadIdx.x + j * kRankThreads;
-    if (e < n) {
-      const int pos = where[j] & 0xffffu, first = where[j] >> 16;
-      const uint32_t low = key[j] & low_mask;
-      where[j] = 0xffffffffu;
-      if (pos > first || (pos + 1 < n && (sk[pos + 1] & low_mask) == low)) {
-        int rank = 0;
-        for (int q = first; q < n; ++q) {
-          const uint32_t kq = sk[q];
-          if ((kq & low_mask) != low) break;
-          const int32_t vq = sv[q];
-          rank += (kq < key[j]) || (kq == key[j] && (vq < val[j] || (vq == val[j] && q < pos)));
-        }
-        if (first + rank != pos) where[j] = static_cast<uint32_t>(first + rank);
-      }
-    }
-  }
-  __syncthreads();
-#pragma unroll
-  for (int j = 0; j < kRankItems; ++j) {
-    if (threadIdx.x + j * kRankThreads < n && where[j] != 0xffffffffu) {
-      sk[where[j]] = key[j];
-      sv[where[j]] = val[j];
-    }
-  }
-  __syncthreads();
+  for (int j = 0; j < kRankItems; ++j)
+    if (threadIdx.x + j * kRankThreads < n && (where[j] & 0x80000000u))
+      list[atomicAdd(&list_n, 1)] = where[j] & 0x7fffffffu;
   for (int i = threadIdx.x; i < n; i += kRankThreads) {
     kout[i] = sk[i];
     vout[i] = sv[i];
   }
-}
+  __syncthreads();
 
+  // Pairs that share a counter (normally: the same row) are ordered by (key, bag id); among equal
+  // pairs the arrival order stands, which cannot be told apart in the output.  A pair whose place
+  // changes overwrites what the copy above put there.
+  const int listed = list_n;
+  for (int li = threadIdx.x; li < listed; li += kRankThreads) {
+    const int pos = list[li] & 0xffffu, first = list[li] >> 16;
+    const uint32_t k0 = sk[pos];
+    const int32_t v0 = sv[pos];
+    const uint32_t low = k0 & low_mask;
+    int rank = 0;
+    for (int q = first; q < n; ++q) {
+      const uint32_t kq = sk[q];
+      if ((kq & low_mask) != low) break;
+      const int32_t vq = sv[q];
+      rank += (kq < k0) || (kq == k0 && (vq < v0 || (vq == v0 && q < pos)));
+    }
+    if (first + rank != pos) {
+      kout[first + rank] = k0;
+      vout[first + rank] = v0;
+    }
+  }
+}
 
 // One stable radix pass of a CTA of W warps over n pairs, on bits [sh, sh + dbits) of the key or,
 // with BY_VAL, of value - vbase.  Every warp owns a contiguous share of the input, counts its
@@ -542,7 +606,7 @@ bool bucket_geometry(int64_t T, int64_t N, int64_t max_rows_per_table, KeyLayout
   if (S < 1) S = 1;
   if (S > 65535 || T > 65535) return false;
   g->slices = static_cast<int>(S);
-  if (2 * T * nb > ws.hist_cap || T * nb + 1 > ws.hist_cap) return false;
+  if (T * S * nb > ws.hist_cap || T * nb + 1 > ws.hist_cap) return false;
   return true;
 }
 
@@ -551,43 +615,41 @@ int bucket_sort_plan(const int32_t* indices, const int32_t* offsets, int64_t T, 
   const dim3 grid(static_cast<unsigned>(g.slices), static_cast<unsigned>(T));
   const int qcap = static_cast<int>(ws.queue_cap);
   int32_t* queue_count = ws.counters + 8;
-  int32_t* totals = ws.hist;
-  int32_t* reserved = ws.hist + T * g.nb;
   // (key, bag id) pairs between the two levels; keys_in and vals_in are adjacent in the workspace
   uint2* pairs = reinterpret_cast<uint2*>(ws.keys_in);
   const int words = rank_words(g.shift);
-  const size_t rank_smem = static_cast<size_t>(words) * 4 + static_cast<size_t>(kBucketSortCapacity) * 8;
+  const int region_words = words > kBucketSortCapacity ? words : kBucketSortCapacity;  // counters, then a list
+  const size_t rank_smem = static_cast<size_t>(region_words) * 4 + static_cast<size_t>(kBucketSortCapacity) * 8;
   int dev = 0;
   TBE_CUDA_TRY(cudaGetDevice(&dev));
   static std::atomic<bool> opted_in[64];
   if (dev < 64 && !opted_in[dev].load(std::memory_order_acquire)) {
     TBE_CUDA_TRY(cudaFuncSetAttribute(bucket_rank_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      kRankWords * 4 + kBucketSortCapacity * 8));
+                                      (kRankWords > kBucketSortCapacity ? kRankWords : kBucketSortCapacity) * 4 +
+                                          kBucketSortCapacity * 8));
     opted_in[dev].store(true, std::memory_order_release);
   }
-  TBE_CUDA_TRY(cudaMemsetAsync(totals, 0, static_cast<size_t>(2 * T * g.nb) * 4, stream));
-  TBE_CUDA_TRY(cudaMemsetAsync(queue_count, 0, 4, stream));
   {
     KernelTimer timer("bucket_count_kernel", stream);
     bucket_count_kernel<<<grid, kCountThreads, 0, stream>>>(indices, offsets, static_cast<int32_t>(B), g.shift, g.nb,
-                                                            totals);
+                                                            ws.hist, queue_count);
   }
   TBE_CHECK_LAUNCH("bucket_count_kernel");
   {
     KernelTimer timer("bucket_scatter_kernel", stream);
     bucket_scatter_kernel<<<grid, kScatterThreads, 0, stream>>>(indices, offsets, static_cast<int32_t>(B), T,
-                                                                layout.idx_bits, g.shift, g.nb, totals, reserved,
+                                                                layout.idx_bits, g.shift, g.nb, ws.hist,
                                                                 ws.bucket_start, pairs);
   }
   TBE_CHECK_LAUNCH("bucket_scatter_kernel");
   {
     KernelTimer timer("bucket_rank_kernel", stream);
     bucket_rank_kernel<<<static_cast<unsigned>(T * g.nb), kRankThreads, rank_smem, stream>>>(
-        ws.bucket_start, pairs, ws.keys, ws.vals, g.shift, words, queue_count, ws.oversize, qcap);
+        ws.bucket_start, pairs, ws.keys, ws.vals, g.shift, words, region_words, queue_count, ws.oversize, qcap);
   }
   TBE_CHECK_LAUNCH("bucket_rank_kernel");
   {
-    int blocks = 2 * device_sm_count();
+    int blocks = device_sm_count();
     if (blocks > qcap) blocks = qcap;
     int bag_bits = 0;
     while ((1ll << bag_bits) < B) ++bag_bits;
