@@ -49,16 +49,21 @@ def measured_peaks():
 
 # ------------------------------------------------------------------ clocks
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    """Samples nvidia-smi clocks and throttle reasons every 200 ms.  Only samples whose timestamp
+    falls inside the marked window count: the window opens with the timed region and the caller keeps
+    the same steps running until it is long enough (1.5 s) for the 200 ms sampler to see the load."""
 
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    MIN_WINDOW_S = 1.5
 
     def __init__(self, gpu_index):
         self.gpu_index = gpu_index
         self.proc = None
         self.path = None
+        self.t_open = None
+        self.t_close = None
 
     def __enter__(self):
         try:
@@ -71,6 +76,17 @@ class ClockSampler:
             self.proc = None
         return self
 
+    def open_window(self):
+        self.t_open = time.time()
+
+    def close_window(self):
+        self.t_close = time.time()
+
+    def extra_steps(self, ms_per_step):
+        """Steps still to run (untimed) so that the window reaches MIN_WINDOW_S under load."""
+        spent = time.time() - self.t_open
+        return max(0, int((self.MIN_WINDOW_S - spent) / max(ms_per_step * 1e-3, 1e-6)) + 1) if spent < self.MIN_WINDOW_S else 0
+
     def __exit__(self, *exc):
         if self.proc is not None:
             self.proc.terminate()
@@ -79,8 +95,18 @@ class ClockSampler:
             except subprocess.TimeoutExpired:
                 self.proc.kill()
 
+    @staticmethod
+    def _stamp(text):
+        import datetime
+        try:
+            return datetime.datetime.strptime(text, "%Y/%m/%d %H:%M:%S.%f").timestamp()
+        except ValueError:
+            return None
+
     def summary(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0,
+               "window": "timed region plus identical untimed steps, %.1f s under load, sampled every 200 ms"
+                         % ((self.t_close or 0) - (self.t_open or 0))}
         if not self.path or not os.path.exists(self.path):
             return out
         sm, smax, reasons = [], [], set()
@@ -90,6 +116,11 @@ class ClockSampler:
                 parts = [p.strip() for p in line.split(",")]
                 if len(parts) < 9:
                     continue
+                stamp = self._stamp(parts[0])
+                if stamp is not None and self.t_open is not None and self.t_close is not None:
+                    # nvidia-smi stamps the end of its 200 ms interval
+                    if stamp < self.t_open + 0.1 or stamp > self.t_close + 0.05:
+                        continue
                 try:
                     sm.append(float(parts[1]))
                     smax.append(float(parts[2]))
@@ -268,13 +299,24 @@ def run_ours(args, rank, world, local_rank):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    for i in range(args.warmup):
-        step(i)
-    launches0 = _lib.lib().tbe_kernel_launch_count()
     with ClockSampler(local_rank) as clocks:
+        for i in range(args.warmup):
+            step(i)
+        launches0 = _lib.lib().tbe_kernel_launch_count()
+        torch.cuda.synchronize()
+        clocks.open_window()
         total_ms = timed(args.steps)
-    launches = _lib.lib().tbe_kernel_launch_count() - launches0
-    ms_per_step = total_ms / args.steps
+        launches = _lib.lib().tbe_kernel_launch_count() - launches0
+        ms_per_step = total_ms / args.steps
+        # keep the same load on, untimed, until the clock sampler has had 1.5 s of it (every rank runs
+        # the same number of steps: ms_per_step is the maximum over ranks)
+        extra = torch.tensor([clocks.extra_steps(ms_per_step)], device=device)
+        if world > 1:
+            dist.all_reduce(extra, op=dist.ReduceOp.MAX)
+        for i in range(int(extra.item())):
+            step(i)
+        torch.cuda.synchronize()
+        clocks.close_window()
     value = N * world / (ms_per_step * 1e-3)
 
     # second, identical pass with per-launch events for the per-kernel breakdown
@@ -434,12 +476,18 @@ def run_cached(args):
     launches0 = _lib.lib().tbe_kernel_launch_count()
     hit = []
     with ClockSampler(0) as clocks:
+        torch.cuda.synchronize()
+        clocks.open_window()
         start.record()
         for i in range(args.steps):
             step(i)
         stop.record()
         torch.cuda.synchronize()
-    ms = start.elapsed_time(stop) / args.steps
+        ms = start.elapsed_time(stop) / args.steps
+        for i in range(clocks.extra_steps(ms)):
+            step(i)
+        torch.cuda.synchronize()
+        clocks.close_window()
     launches = _lib.lib().tbe_kernel_launch_count() - launches0
     _lib.kernel_timing_enable(True)
     for i in range(args.steps):

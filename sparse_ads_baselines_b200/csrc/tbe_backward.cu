@@ -746,20 +746,27 @@ __global__ void __launch_bounds__(kBwdThreads) long_run_kernel(const BwdArgs a) 
       acc_t acc[NE];
 #pragma unroll
       for (int k = 0; k < NE; ++k) acc[k] = 0;
-      for (int i = gid; i < len; i += groups * 4) {  // four gradient rows in flight per lane
-        uint32_t bag[4];
+      // four gradient rows in flight per lane; the bag ids of the next four are requested before
+      // these rows are waited for, so the only dependent load per round is the gradient row itself
+      uint32_t bag[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int iu = gid + u * groups;
+        bag[u] = iu < len ? static_cast<uint32_t>(__ldg(a.vals + s + iu)) : 0u;
+      }
+      for (int i = gid; i < len; i += groups * 4) {
         Raw<VB> r[4];
         acc_t sc[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int iu = i + u * groups;
-          bag[u] = iu < len ? static_cast<uint32_t>(__ldg(a.vals + s + iu)) : 0u;
-        }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           r[u] = raw_zero<VB>();
           sc[u] = 1;
           if (i + u * groups < len && vact) r[u] = load_grad<T, VB, MEAN>(a, bag[u], v, keep, &sc[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int iu = i + (u + 4) * groups;
+          bag[u] = iu < len ? static_cast<uint32_t>(__ldg(a.vals + s + iu)) : 0u;
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) add_grad<T, VB, MEAN>(r[u], sc[u], acc);
@@ -863,7 +870,13 @@ int launch_runs(const BwdArgs& a, cudaStream_t stream) {
   TBE_CHECK_LAUNCH("run_kernel");
   {
     KernelTimer timer("long_run_kernel", stream);
-    long_run_kernel<T, VB, OPT, MEAN, SR><<<device_sm_count() * 2, kBwdThreads, 0, stream>>>(a);
+    // one CTA per queued run, as many CTAs as fit: the gradient rows of a long run come from L2 and a
+    // CTA keeps only a few KB of them in flight
+    int long_per_sm = 0;
+    TBE_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&long_per_sm, long_run_kernel<T, VB, OPT, MEAN, SR>,
+                                                               kBwdThreads, 0));
+    if (long_per_sm < 1) long_per_sm = 1;
+    long_run_kernel<T, VB, OPT, MEAN, SR><<<device_sm_count() * long_per_sm, kBwdThreads, 0, stream>>>(a);
   }
   TBE_CHECK_LAUNCH("long_run_kernel");
   return TBE_OK;

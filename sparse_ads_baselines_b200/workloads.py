@@ -50,10 +50,12 @@ WORKLOADS = {
                      index_dist="zipf", zipf_alpha=1.2),
     # table-sharded TBE, 64 tables per GPU over the global batch
     "cfg5": Workload("cfg5", T=64, E=1_000_000, D=128, B=65_536, dtype="fp16", L=32, optimizer="sgd", lr=0.05),
-    # small stand-ins of the same kernels for profiler captures: a 2 GB table (far above L2) and the
-    # target's 33 MB of pooled rows, so DRAM and L2 behave as in the full-size runs
-    "prof": Workload("prof", T=8, E=1_000_000, D=128, B=16_384, dtype="fp16", L=38, optimizer="sgd", lr=0.05),
-    "prof_cfg3": Workload("prof_cfg3", T=8, E=1_000_000, D=128, B=16_384, dtype="fp32", pooling="mean",
+    # Stand-ins of the same kernels for profiler captures: a quarter / an eighth of the tables of the
+    # target / cfg3 with everything per table unchanged (rows, bags, bag lengths, index distribution),
+    # so every kernel sees the same row reuse, sort geometry and 4 GB of tables (far above L2) while
+    # one launch lasts a quarter / an eighth as long.  Per-launch traffic scales by the table count.
+    "prof": Workload("prof", T=16, E=1_000_000, D=128, B=2048, dtype="fp16", L=38, optimizer="sgd", lr=0.05),
+    "prof_cfg3": Workload("prof_cfg3", T=8, E=1_000_000, D=128, B=2048, dtype="fp32", pooling="mean",
                           optimizer="exact_rowwise_adagrad", lr=0.01, eps=1e-8, L_dist="poisson", L_mean=20.0,
                           L_min=1, L_max=100, index_dist="zipf", zipf_alpha=1.05),
     # the headline target: cfg2's shapes with forward + backward + fused exact SGD
