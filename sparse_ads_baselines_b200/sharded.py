@@ -109,11 +109,15 @@ class _FusedShardedLookup(torch.autograd.Function):
         buf = m._buffers_for(indices.device)
         T, B, D = m.local_tables, m.global_batch, m.embedding_dim
         grad = grad.contiguous()
+        # the sort of the lookups needs no gradient: it runs on a side stream under the exchange
+        plan = None
+        if m.tbe.optimizer in (Optimizer.SGD, Optimizer.EXACT_ROWWISE_ADAGRAD):
+            plan = tbe_ext.backward_plan(m.tbe.table_offsets, indices, offsets, weights.size(0))
         with torch.cuda.device(weights.device):
             _lib.call("tbe_all2all_push", grad.data_ptr(), buf.grad_ptrs, buf.world, buf.rank, B // buf.world,
                       T * D * grad.element_size(), tbe_ext._stream(weights.device))
             buf.barrier()
-        m.apply_local_backward(buf.grad_in, indices, offsets)
+        m.apply_local_backward(buf.grad_in, indices, offsets, plan=plan)
         return None, None, None, None
 
 
@@ -144,16 +148,17 @@ class TableShardedEmbeddingBags(nn.Module):
                                            self.group if self.group is not None else dist.group.WORLD)
         return self._symm
 
-    def apply_local_backward(self, grad_local, indices, offsets):
-        """Fused backward + optimizer of the local tables for ``grad_local = [B, T/W, D]``."""
+    def apply_local_backward(self, grad_local, indices, offsets, plan=None):
+        """Fused backward + optimizer of the local tables for ``grad_local = [B, T/W, D]``; ``plan`` is
+        an optional :func:`table_batched_embeddings.backward_plan` of the same lookups."""
         t = self.tbe
         if t.optimizer == Optimizer.SGD:
             tbe_ext.backward_sgd(grad_local, t.embedding_weights.data, t.table_offsets, indices, offsets,
-                                 t.learning_rate, 200, 1, False, pooling_mode=t.pooling_mode)
+                                 t.learning_rate, 200, 1, False, pooling_mode=t.pooling_mode, plan=plan)
         elif t.optimizer == Optimizer.EXACT_ROWWISE_ADAGRAD:
             tbe_ext.backward_exact_adagrad(grad_local, t.embedding_weights.data, t.table_offsets, indices, offsets,
                                            None, t.optimizer_state, t.learning_rate, t.eps, t.stochastic_rounding, 1,
-                                           pooling_mode=t.pooling_mode)
+                                           pooling_mode=t.pooling_mode, plan=plan)
         else:
             tbe_ext.backward_approx_adagrad(grad_local, t.embedding_weights.data, t.table_offsets, indices, offsets,
                                             None, t.optimizer_state, t.learning_rate, t.eps, 200,
