@@ -61,8 +61,13 @@ TBE_API const char* tbe_last_error_string(void);
  * only; CUB sort/select launches are counted separately by tbe_library_launch_count). */
 TBE_API int64_t tbe_kernel_launch_count(void);
 TBE_API int64_t tbe_library_launch_count(void);
-/* Tuning knob for benchmarking sweeps: name in {"fwd_unroll","fwd_threads",
- * "bwd_threads","bwd_unroll","long_segment"}; value 0 restores the default. */
+/* Tuning knob for benchmarking sweeps; value 0 restores the default.  Names:
+ *   fwd_unroll, fwd_threads, fwd_blocks_per_sm   forward: row loads in flight per lane, CTA size, CTAs per SM
+ *   bwd_threads, bwd_blocks_per_sm               backward apply: CTA size, CTAs per SM
+ *   bwd_vpl, bwd_unroll                          backward apply: 16-byte vectors per lane (1/2/4), runs in flight (1/2)
+ *   long_segment                                 run length above which a run gets a CTA of its own
+ *   bwd_sort                                     1: always linearize + device radix sort for the backward plan
+ *   sort_bucket                                  wanted mean bucket size of the table-segmented sort */
 TBE_API int tbe_set_tuning(const char* name, int value);
 
 /* Per-launch timing for benchmarks: while enabled, every kernel launch of this library
