@@ -317,9 +317,17 @@ __device__ __forceinline__ void apply_update(char* wp, const Raw<VB>& wraw, cons
   st_row_hint<VB>(wp, pack_out<T, VB, SR>(w, rng), streaming);
 }
 
-// First position >= lo in the sorted keys whose key differs from `row` (keys[lo-1] == row).
+// First position >= lo in the sorted keys whose key differs from `row` (keys[lo-1] == row).  Most runs
+// end a few entries further on, so the end is bracketed by doubling steps before it is bisected.
 __device__ __forceinline__ int run_end(const uint32_t* __restrict__ keys, int lo, int N, uint32_t row) {
   int hi = N;
+  for (int step = 1; lo + step < N; step <<= 1) {
+    if (__ldg(keys + lo + step - 1) != row) {
+      hi = lo + step - 1;
+      break;
+    }
+    lo += step;
+  }
   while (lo < hi) {
     const int mid = lo + ((hi - lo) >> 1);
     if (__ldg(keys + mid) == row) {
@@ -721,6 +729,8 @@ __global__ void __launch_bounds__(kBwdThreads) long_run_kernel(const BwdArgs a) 
   using acc_t = typename Acc<T>::type;
   constexpr int NE = VB / sizeof(T);
   __shared__ acc_t part[kBwdThreads * NE];
+  __shared__ int64_t entry_off[kBwdThreads];   // byte offset of the gradient row of an entry
+  __shared__ acc_t entry_scale[kBwdThreads];   // 1/L of its bag (mean pooling)
   const int lane = threadIdx.x & 31;
   const int lpr_log2 = a.lpr1_log2;
   const int lpr = 1 << lpr_log2;
@@ -739,37 +749,47 @@ __global__ void __launch_bounds__(kBwdThreads) long_run_kernel(const BwdArgs a) 
     char* wrow = static_cast<char*>(a.weights) + static_cast<int64_t>(row) * row_bytes;
 
     // Folds the groups' partial sums for chunk c in group order; every thread of warp 0 ends with the
-    // total of its own `sub`.
+    // total of its own `sub`.  The run is taken 256 entries at a time: every thread first turns one
+    // entry's bag id into the offset of its gradient row (and 1/L for mean pooling) and leaves it in
+    // shared memory, then group g sums entries g, g + groups, ... with eight row loads in flight and
+    // no load depending on another.
     auto reduce_chunk = [&](int c, acc_t* total) {
       const int v = (c << 5) + sub;
       const bool vact = v < a.nvec;
       acc_t acc[NE];
 #pragma unroll
       for (int k = 0; k < NE; ++k) acc[k] = 0;
-      // four gradient rows in flight per lane; the bag ids of the next four are requested before
-      // these rows are waited for, so the only dependent load per round is the gradient row itself
-      uint32_t bag[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int iu = gid + u * groups;
-        bag[u] = iu < len ? static_cast<uint32_t>(__ldg(a.vals + s + iu)) : 0u;
-      }
-      for (int i = gid; i < len; i += groups * 4) {
-        Raw<VB> r[4];
-        acc_t sc[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          r[u] = raw_zero<VB>();
-          sc[u] = 1;
-          if (i + u * groups < len && vact) r[u] = load_grad<T, VB, MEAN>(a, bag[u], v, keep, &sc[u]);
+      for (int base = 0; base < len; base += kBwdThreads) {
+        const int m = min(kBwdThreads, len - base);
+        __syncthreads();  // the previous block of entries has been consumed
+        if (static_cast<int>(threadIdx.x) < m) {
+          const uint32_t bag = static_cast<uint32_t>(__ldg(a.vals + s + base + threadIdx.x));
+          const uint32_t t = fastdiv(bag, a.divB);
+          const uint32_t b = bag - t * static_cast<uint32_t>(a.B);
+          entry_off[threadIdx.x] = (static_cast<int64_t>(b) * a.stride_b + static_cast<int64_t>(t) * a.stride_t) *
+                                   static_cast<int64_t>(sizeof(T));
+          if (MEAN)
+            entry_scale[threadIdx.x] =
+                acc_t(1) / static_cast<acc_t>(__ldg(a.offsets + bag + 1) - __ldg(a.offsets + bag));
         }
+        __syncthreads();
+        for (int i = gid; i < m; i += groups * 8) {
+          Raw<VB> r[8];
+          acc_t sc[8];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int iu = i + (u + 4) * groups;
-          bag[u] = iu < len ? static_cast<uint32_t>(__ldg(a.vals + s + iu)) : 0u;
+          for (int u = 0; u < 8; ++u) {
+            const int iu = i + u * groups;
+            r[u] = raw_zero<VB>();
+            sc[u] = 1;
+            if (iu < m && vact) {
+              r[u] = ld_stream_hint<VB>(static_cast<const char*>(a.grad) + entry_off[iu] + static_cast<int64_t>(v) * VB,
+                                        keep);
+              if (MEAN) sc[u] = entry_scale[iu];
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) add_grad<T, VB, MEAN>(r[u], sc[u], acc);
         }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) add_grad<T, VB, MEAN>(r[u], sc[u], acc);
       }
       __syncthreads();  // previous use of `part` finished
 #pragma unroll
