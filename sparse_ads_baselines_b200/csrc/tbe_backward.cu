@@ -374,7 +374,7 @@ __device__ __forceinline__ Tile load_tile(const uint32_t* __restrict__ keys, con
 // runs in flight: the weight row, the optimizer state and the first two gradient rows of each are
 // requested first, then the runs are finished one after the other.
 template <typename T, int VB, int OPT, bool MEAN, bool SR, int SEGS, int VPL>
-__global__ void __launch_bounds__(kBwdThreads) run_kernel(const BwdArgs a) {
+__global__ void __launch_bounds__(kBwdThreads, 4) run_kernel(const BwdArgs a) {
   using acc_t = typename Acc<T>::type;
   constexpr int NE = VB / sizeof(T);
   const int lane = threadIdx.x & 31;

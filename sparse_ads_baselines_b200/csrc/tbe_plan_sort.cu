@@ -507,11 +507,16 @@ __device__ __forceinline__ void radix_pass(const uint32_t* sk, const int32_t* sv
     }
   }
   __syncthreads();
+  // the next round's pair is requested before this round's is ranked
+  uint32_t key_next = ca + lane < cb ? sk[ca + lane] : 0u;
+  int32_t val_next = ca + lane < cb ? sv[ca + lane] : vbase;
   for (int32_t p0 = ca; p0 < cb; p0 += 32) {
     const int32_t p = p0 + lane;
     const bool valid = p < cb;
-    const uint32_t key = valid ? sk[p] : 0u;
-    const int32_t val = valid ? sv[p] : vbase;
+    const uint32_t key = key_next;
+    const int32_t val = val_next;
+    key_next = p + 32 < cb ? sk[p + 32] : 0u;
+    val_next = p + 32 < cb ? sv[p + 32] : vbase;
     const uint32_t d = ((BY_VAL ? static_cast<uint32_t>(val - vbase) : key) >> sh) & mask;
     uint32_t peers = __ballot_sync(0xffffffffu, valid);
     for (int bit = 0; bit < dbits; ++bit) {
