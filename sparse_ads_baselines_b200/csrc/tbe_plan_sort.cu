@@ -7,12 +7,15 @@
 // the index inside the table needs ordering, and a table sees far fewer lookups than it has rows.
 // This file orders every table independently in two levels that stay in L2:
 //
-//   1. bucket_count_kernel   : lookups per (table, bucket), bucket = index >> shift.
-//   2. bucket_scatter_kernel : every (slice, table) CTA reserves room in each bucket for the lookups
-//                              of its position range and moves (key, bag id) there.  The bag id of a
+//   1. bucket_count_kernel   : a table's positions are cut into slices; lookups per (table, slice,
+//                              bucket), bucket = index >> shift.
+//   2. bucket_scatter_kernel : every (slice, table) CTA works out from the histograms where its
+//                              slice's share of each bucket lies (slices in order, no global
+//                              atomics) and moves (key, bag id) pairs there.  The bag id of a
 //                              position comes from a running search in `offsets`, so this kernel
 //                              also replaces the separate linearize pass.  The order inside a
-//                              bucket is whatever the atomics gave; level 2 makes that irrelevant.
+//                              slice's share is whatever the shared-memory atomics gave; level 2
+//                              makes that irrelevant.
 //   3. bucket_rank_kernel    : one CTA per bucket.  A counting sort on the low `shift` index bits in
 //                              shared memory (one 16-bit counter per possible row of the bucket)
 //                              brings equal rows together; pairs that share a row are then ranked
