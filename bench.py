@@ -338,10 +338,10 @@ def run_ours(args, rank, world, local_rank):
     U_mean = sum(b["U"] for b in batches) / ROTATE
     alg = workloads.algorithmic_bytes(w, N, U_mean, nbags, backward)
     kernel_bytes = {"tbe_forward_kernel": alg["fwd"], "run_kernel": alg["bwd"]}
-    # DRAM bytes per lookup of the two big kernels from the committed ncu capture of the `prof`
-    # workload (profiles/run_kernel_prof.md, profiles/tbe_forward_kernel_prof.md): a quarter of the
-    # target's tables with the same rows, bags and lengths per table, so traffic grows with the
-    # lookups.  Only workloads of that per-table shape get a figure.
+    # DRAM bytes per lookup of the two big kernels from the ncu capture of the `prof` workload that is
+    # summarised under profiles/: a quarter of the target's tables with the same rows, bags and
+    # lengths per table, so traffic grows with the lookups.  Only workloads of that per-table shape
+    # get a figure.
     measured_traffic_per_lookup = {"run_kernel": 464.05, "tbe_forward_kernel": 254.65}
     same_shape_as_prof = (w.E, w.D, w.B, w.L, w.dtype, w.index_dist, w.L_dist) == (1_000_000, 128, 2048, 38, "fp16",
                                                                                    "uniform", "fixed")

@@ -76,6 +76,9 @@ def _table_sort_case(rng, T, E, B, Lmax, hot):
     (70, 300000, 64, 30, False),       # more tables than one slice each can fill
     (1, 2 ** 20, 3000, 50, False),
     (3, 2 ** 20 + 1, 1500, 50, True),  # index bits roll over to 21
+    (1, 2 ** 24, 4096, 20, False),     # 1024 buckets of 2^14 rows: the most the two-level sort takes
+    (1, 2 ** 24 + 1, 4096, 20, False), # one more row: falls back to the device radix sort
+    (300, 5000, 8, 12, False),         # more tables than resident CTAs: one slice per table
 ])
 def test_table_segmented_sort_exact(cuda_device, T, E, B, Lmax, hot):
     """With max_rows_per_table the plan comes from the table-segmented two-level sort; rows, bags and
