@@ -34,7 +34,7 @@ enum Tuning {
   kTuneBwdVpl,
   kTuneBwdSort,     // 0: two-level bucket sort when the batch suits it, 1: always the device radix sort
   kTuneSortBucket,  // wanted mean bucket size of the two-level sort (0: default)
-  kTuneBwdPrefetch,  // 1: the backward does not prefetch a tile's weight rows into L2
+  kTuneBwdPrefetch,  // backward L2 prefetch of a tile's weight rows: 0 = rows up to 256 bytes, 1 = never, 2 = always
   kTuneCount
 };
 
