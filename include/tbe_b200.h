@@ -67,8 +67,7 @@ TBE_API int64_t tbe_library_launch_count(void);
  *   bwd_vpl, bwd_unroll                          backward apply: 16-byte vectors per lane (1/2/4), runs in flight (1/2)
  *   long_segment                                 run length above which a run gets a CTA of its own
  *   bwd_sort                                     1: always linearize + device radix sort for the backward plan
- *   sort_bucket                                  wanted mean bucket size of the table-segmented sort
- *   bwd_prefetch                                 backward L2 prefetch of a tile's weight rows: 0 rows <= 256 B, 1 never, 2 always */
+ *   sort_bucket                                  wanted mean bucket size of the table-segmented sort */
 TBE_API int tbe_set_tuning(const char* name, int value);
 
 /* Per-launch timing for benchmarks: while enabled, every kernel launch of this library

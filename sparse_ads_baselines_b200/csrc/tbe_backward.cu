@@ -234,7 +234,6 @@ struct BwdArgs {
   int32_t lpr1_log2, nchunks;  // wide / long-run kernels: one vector per lane, rows walked in chunks
   int32_t nvec;
   int32_t long_threshold;
-  int32_t prefetch_bytes;  // leading bytes of every weight row requested from L2 at the start of a tile
   float lr, eps;
   uint64_t sr_seed, sr_offset;
 };
@@ -446,13 +445,6 @@ __global__ void __launch_bounds__(kBwdThreads, 4) run_kernel(const BwdArgs a) {
     const uint32_t key0 = __shfl_sync(kFullMask, cur.key, 0);
     const int32_t val0 = __shfl_sync(kFullMask, cur.val, 0);
     const uint32_t my_row = key_to_row(a.table_offsets, a.idx_bits, valid ? cur.key : key0);
-    // The weight rows of all runs that start in the tile are requested from L2 now, one lane per run:
-    // DRAM sees a whole tile's rows at once, while the register-held loads below, a few rows per
-    // warp at a time, then find them in L2.
-    if (is_start) {
-      const char* wrow = wbase + static_cast<uint64_t>(my_row) * row_bytes;
-      for (int off = 0; off < a.prefetch_bytes; off += 128) prefetch_l2(wrow + off);
-    }
     acc_t my_scale = 1;
     const uint32_t my_goff = grad_units(static_cast<uint32_t>(valid ? cur.val : val0), &my_scale);
     unsigned mine = smask & own_lanes;
@@ -992,13 +984,6 @@ int exact_backward(int opt, const void* grad, int64_t stride_b, int64_t stride_t
   a.nvec = g.nvec;
   a.nchunks = g.nchunks;
   a.long_threshold = tuning(kTuneLongSegment) > 0 ? tuning(kTuneLongSegment) : kDefaultLongSegment;
-  // measured on B200: asking L2 for a tile's rows up front takes 8 us off the 480 us of the headline
-  // launch (256-byte rows) and adds 40 us to config 3's (512-byte rows, hot rows already in L2)
-  {
-    const int row_bytes = g.nvec * g.vb, knob = tuning(kTuneBwdPrefetch);
-    const bool on = knob == 2 || (knob != 1 && row_bytes <= 256);
-    a.prefetch_bytes = on ? (row_bytes < 1024 ? row_bytes : 1024) : 0;
-  }
   a.lr = lr;
   a.eps = eps;
   a.sr_seed = sr_seed;

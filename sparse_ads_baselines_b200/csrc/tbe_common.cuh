@@ -34,7 +34,6 @@ enum Tuning {
   kTuneBwdVpl,
   kTuneBwdSort,     // 0: two-level bucket sort when the batch suits it, 1: always the device radix sort
   kTuneSortBucket,  // wanted mean bucket size of the two-level sort (0: default)
-  kTuneBwdPrefetch,  // backward L2 prefetch of a tile's weight rows: 0 = rows up to 256 bytes, 1 = never, 2 = always
   kTuneCount
 };
 
@@ -196,9 +195,6 @@ __device__ __forceinline__ uint64_t l2_policy_evict_normal() {
   asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
   return p;
 }
-// Asks L2 for the 128-byte line at p without tying up a register.
-__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
-
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
