@@ -330,7 +330,11 @@ def test_full_size_target_step_properties(cuda_device):
     grad = (torch.randn(w.B, w.T, w.D, device=dev, generator=gen) * 0.01).half()
     to = torch.arange(w.T, dtype=torch.int32, device=dev) * w.E
     idx, off = torch.from_numpy(indices).to(dev), torch.from_numpy(offsets).to(dev)
-    rows, bags, starts = tbe.sort_segments(to, idx, off, w.T * w.E)
+    # the table-segmented sort (the plan backward_sgd uses below) against the device radix sort
+    rows, bags, starts = tbe.sort_segments(to, idx, off, w.T * w.E, max_rows_per_table=w.E)
+    rows_r, bags_r, starts_r = tbe.sort_segments(to, idx, off, w.T * w.E)
+    assert torch.equal(rows, rows_r) and torch.equal(bags, bags_r) and torch.equal(starts, starts_r)
+    del rows_r, bags_r, starts_r
     assert starts.numel() == workloads.count_unique_rows(indices, offsets, w.T, w.B, w.E)
     assert bool((rows[1:] >= rows[:-1]).all())
     before = weights.clone()
