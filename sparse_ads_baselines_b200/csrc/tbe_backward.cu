@@ -116,7 +116,7 @@ KeyLayout key_layout(int64_t T, int64_t total_rows, int64_t max_rows_per_table, 
 
 int check_sizes(const char* who, int64_t T, int64_t B, int64_t N, int64_t total_rows) {
   TBE_REQUIRE(T > 0 && B > 0, "%s: T and B must be > 0", who);
-  TBE_REQUIRE(N >= 0 && N < (1ll << 31) - 64, "%s: N out of range", who);
+  TBE_REQUIRE(N >= 0 && N < (1ll << 31) - 65536, "%s: N out of range", who);  // kernels look a tile ahead in int32
   TBE_REQUIRE(T * B < (1ll << 31), "%s: B*T out of range", who);
   TBE_REQUIRE(total_rows > 0 && total_rows < (1ll << 31), "%s: total_rows out of range", who);
   return TBE_OK;
@@ -321,7 +321,7 @@ __device__ __forceinline__ void apply_update(char* wp, const Raw<VB>& wraw, cons
 // end a few entries further on, so the end is bracketed by doubling steps before it is bisected.
 __device__ __forceinline__ int run_end(const uint32_t* __restrict__ keys, int lo, int N, uint32_t row) {
   int hi = N;
-  for (int step = 1; lo + step < N; step <<= 1) {
+  for (int step = 1; step < (1 << 30) && static_cast<int64_t>(lo) + step < N; step <<= 1) {
     if (__ldg(keys + lo + step - 1) != row) {
       hi = lo + step - 1;
       break;
