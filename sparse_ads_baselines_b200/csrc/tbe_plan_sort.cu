@@ -249,25 +249,48 @@ __global__ void __launch_bounds__(kScatterThreads, 3) bucket_scatter_kernel(
       index[r] = pn < cb ? __ldg(indices + pn) : 0;
     }
     if (wa < cb) {
+      // bag of p = cur + number of bag ends that are <= p
+      const int32_t last_p = min(cb, wa + 32 * kRounds) - 1;
+      if (__shfl_sync(0xffffffffu, ends, 31) > last_p) {
+        // Usual case: the window of 32 bag ends reaches past the step.  Ends at or before the
+        // step's first position count for all of its positions; the few ends inside the step are
+        // broadcast one by one and compared with the lane's positions.
+        const int32_t first_bag = cur + __popc(__ballot_sync(0xffffffffu, ends <= wa));
+        unsigned inside = __ballot_sync(0xffffffffu, ends > wa && ends <= last_p);
 #pragma unroll
-      for (int r = 0; r < kRounds; ++r) {
-        const int32_t p = wa + r * 32 + lane;
-        const bool valid = p < cb;
-        // bag of p = cur + number of bag ends that are <= p
-        int32_t bag = -1, from = cur, window = ends;
-        while (true) {
-          const int c = count_not_above(window, p);
-          if (bag < 0 && valid && c < 32) bag = from + c;
-          if (__all_sync(0xffffffffu, bag >= 0 || !valid)) break;
-          from += 32;  // more than 32 bags end inside these 32 positions (short or empty bags)
-          window = load_bag_ends(offsets, from, bag_hi, lane);
+        for (int r = 0; r < kRounds; ++r) bagv[r] = first_bag;
+        while (inside) {
+          const int32_t e = __shfl_sync(0xffffffffu, ends, __ffs(inside) - 1);
+          inside &= inside - 1u;
+#pragma unroll
+          for (int r = 0; r < kRounds; ++r) bagv[r] += (wa + r * 32 + lane >= e) ? 1 : 0;
         }
-        const int32_t tail = __shfl_sync(0xffffffffu, bag, 31);
-        if (tail - cur >= 16) {  // slide the window before it runs out (tail is -1 past the share's end)
+        const int32_t tail = cur + __popc(__ballot_sync(0xffffffffu, ends <= last_p));  // bag of last_p
+        if (tail - cur >= 16) {  // slide the window before it runs out
           cur = tail;
           ends = load_bag_ends(offsets, cur, bag_hi, lane);
         }
-        bagv[r] = bag;
+      } else {
+        // short or empty bags: more than the window's bags end inside the step
+#pragma unroll
+        for (int r = 0; r < kRounds; ++r) {
+          const int32_t p = wa + r * 32 + lane;
+          const bool valid = p < cb;
+          int32_t bag = -1, from = cur, window = ends;
+          while (true) {
+            const int c = count_not_above(window, p);
+            if (bag < 0 && valid && c < 32) bag = from + c;
+            if (__all_sync(0xffffffffu, bag >= 0 || !valid)) break;
+            from += 32;
+            window = load_bag_ends(offsets, from, bag_hi, lane);
+          }
+          const int32_t tail = __shfl_sync(0xffffffffu, bag, 31);
+          if (tail - cur >= 16) {  // (tail is -1 past the share's end)
+            cur = tail;
+            ends = load_bag_ends(offsets, cur, bag_hi, lane);
+          }
+          bagv[r] = bag;
+        }
       }
     }
     __syncthreads();
