@@ -7,17 +7,24 @@ of ``bench.py`` -- never by the product package, which has no CPU path.
 The arithmetic of the pooled lookup lives in a third-party dependency of the reference, PyTorch
 (this container pins torch 2.11.0+cu128): the reference's own tests use per-table
 ``torch.nn.EmbeddingBag(E, D, mode="sum", sparse=True)`` as their oracle
-(test_table_batched_embeddings.py:127,138-141,174,186,238,255-260), and so does this file.  The
-reference ships no golden vectors (every test draws fresh random inputs), and its CUDA extension
-cannot be built here, so parity is pinned by the formulas of those tests:
+(test_table_batched_embeddings.py:127,138-141,174,186,238,255-260), and so does this file, following
+the formulas of those tests:
   forward          test_table_batched_embeddings.py:115-160
   SGD              test_table_batched_embeddings.py:163-216   (w - lr * grad)
   rowwise Adagrad  test_table_batched_embeddings.py:296-318   (state = sum_d grad^2,
                                                                w - lr * grad / (sqrt(state) + eps))
-Parts with no counterpart in the reference's tests -- mean pooling, SGD on repeated rows, the
-all-to-all layout, the row cache -- are parity unpinned by the reference and pinned here by
-EmbeddingBag(mode="mean"), by ``w - lr * grad.to_dense()``, by the layout formula of
-sparse_embedding_cuda.cpp:475-532 and by this file's own cache model.
+
+Parity is PINNED by the reference itself: ``oracle/build_ref.py`` builds the reference's
+``table_batched_embeddings`` extension from its own sources (kernels unmodified),
+``tests/golden/make_reference_golden.py`` ran it on a B200 and stored its outputs as
+``tests/golden/reference_*.npz``, and ``tests/test_oracle_reference_pin.py`` checks every function
+below that has a counterpart there (forward, weighted forward, SGD, exact and approximate rowwise
+Adagrad with state and per-sample-weight gradient, mixed widths, construct_offsets) against them.
+The reference ships no golden vectors of its own (every test draws fresh random inputs).
+Parts with no counterpart in the reference -- mean pooling, SGD on repeated rows (the reference
+races), the all-to-all layout (its test asserts nothing), the row cache -- remain unpinned by it
+and are pinned here by EmbeddingBag(mode="mean"), by ``w - lr * grad.to_dense()``, by the layout
+formula of sparse_embedding_cuda.cpp:475-532 and by this file's own cache model.
 """
 import numpy as np
 import torch
