@@ -129,6 +129,26 @@ TBE_API int tbe_forward_sharded(const void* weights, const int32_t* table_offset
 TBE_API int tbe_all2all_push(const void* src, void* const* peer_dst, int world, int rank,
                              int64_t rows_local, int64_t chunk_bytes, void* stream);
 
+/* Ordering between ranks for the two exchange kernels above, without a collective: every rank owns a
+ * flag array int32 [world] that all peers can write (peer-mapped, zero-initialised before first
+ * use); rank r writes slot r of every peer's array.  One launch of one small CTA does, per peer j,
+ *   signal: if peer_flags != NULL, store signal_value to peer_flags[j][rank] with release semantics at
+ *           system scope -- after everything enqueued earlier on `stream`, peer stores included;
+ *   wait:   if local_flags != NULL, poll local_flags[j] until it is >= wait_value (step numbers only
+ *           grow).  The poll is bounded: after timeout_ns it writes {TBE_ERR_TIMEOUT, j, wait_value,
+ *           last value seen} to status (device int32 [4], zero = no error; only the first timeout is
+ *           kept) and returns, so a rank that died or never joined costs a timeout, never a hung GPU.
+ * A barrier after a producer kernel is signal_value = wait_value = step.  Kernels launched later on
+ * `stream` run after the wait returns (timed out or not): read status before trusting their results.
+ * tbe_peer_status copies status to host_out4, SYNCHRONISES the stream and returns TBE_ERR_TIMEOUT
+ * (with the peer and steps in the error string) if a wait ran out.
+ * replaces the ncclGroupStart/ncclSend/ncclRecv/ncclGroupEnd ordering of forward_all2all_nccl
+ * (sparse_embedding_cuda.cpp:488-523), which the fused exchange has no collective call to inherit. */
+TBE_API int tbe_peer_signal_wait(void* const* peer_flags, const int32_t* local_flags, int world, int rank,
+                                 int32_t signal_value, int32_t wait_value, int64_t timeout_ns,
+                                 int32_t* status, void* stream);
+TBE_API int tbe_peer_status(const int32_t* status, int32_t* host_out4, void* stream);
+
 /* ---- backward with the optimizer fused into the write-back -------------- */
 
 /* Scratch bytes the backward calls need for N indices over total_rows rows. */
@@ -266,7 +286,7 @@ TBE_API int tbe_check_inputs(const int32_t* indices, const int32_t* offsets,
 
 /* Managed allocation preferred on the host and mapped for the current device
  * (replaces CUDAManagedAllocator, table_batched_embeddings_cuda.cu:797-812), and a
- * pinned, write-combined, device-mapped host allocation returning both addresses
+ * pinned, device-mapped host allocation (not write-combined: the optimizer reads the rows back) returning both addresses
  * (replaces CUDAHostMappedAllocator, :820-838).  These DO allocate; free with the
  * matching call. */
 TBE_API int tbe_alloc_managed(void** ptr, int64_t bytes);

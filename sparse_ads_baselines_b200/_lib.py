@@ -30,6 +30,8 @@ SIGNATURES = {
     "tbe_forward_sharded": (_i32, [_vp, _vp, _vp, _vp, _vp, ctypes.POINTER(_vp), _i32, _i64, _i64, _i64, _i64,
                                    _i64, _i32, _i32, _vp]),
     "tbe_all2all_push": (_i32, [_vp, ctypes.POINTER(_vp), _i32, _i32, _i64, _i64, _vp]),
+    "tbe_peer_signal_wait": (_i32, [ctypes.POINTER(_vp), _vp, _i32, _i32, _i32, _i32, _i64, _vp, _vp]),
+    "tbe_peer_status": (_i32, [_vp, ctypes.POINTER(ctypes.c_int32), _vp]),
     "tbe_backward_workspace_bytes": (_i64, [_i64, _i64]),
     "tbe_backward_plan": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     "tbe_backward_sgd": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _i32,

@@ -38,7 +38,8 @@ namespace {
 
 constexpr int kCountThreads = 512;
 constexpr int kScatterThreads = 512;
-constexpr int kScatterTile = 2048;  // positions a CTA gathers in shared memory at a time
+constexpr int kScatterTile = 2048;      // positions a CTA gathers in shared memory at a time ...
+constexpr int kScatterTileWide = 4096;  // ... when a table has more than kFewBuckets buckets
 constexpr int kRankThreads = 256;
 constexpr int kRankItems = kBucketSortCapacity / kRankThreads;  // pairs a thread holds
 constexpr int kRankBits = 14;                                   // most index bits level 2 can count on
@@ -46,7 +47,10 @@ constexpr int kRankWords = (1 << kRankBits) / 2;                // two 16-bit co
 constexpr int kOversizeThreads = 1024;
 constexpr int kOversizeWarps = kOversizeThreads / 32;
 constexpr int kMaxDigits = 256;             // radix passes look at up to 8 bits
-constexpr int kMaxBuckets = 1024;           // buckets per table
+constexpr int kFewBuckets = 1024;           // buckets per table the narrow kernel variants hold in shared memory
+constexpr int kMaxBuckets = 4096;           // buckets per table (wide variants: busy tables, e.g. 2 lookups per row)
+constexpr int kBucketIdBits = 12;           // log2(kMaxBuckets)
+static_assert((1 << kBucketIdBits) == kMaxBuckets && kScatterTileWide <= (1 << (31 - kBucketIdBits)), "slot packing");
 constexpr int kDefaultBucketTarget = 1400;  // wanted mean bucket size
 static_assert(kBucketSortCapacity % kRankThreads == 0 && kBucketSortCapacity < 65536, "16-bit positions");
 
@@ -96,11 +100,12 @@ __device__ __forceinline__ V cta_exclusive_scan(V x, V* warp_tot, bool warp_acti
 }
 
 // hist[(t * S + s) * nb + bucket] = lookups of slice s of table t that fall in the bucket.
+template <int NBCAP>
 __global__ void __launch_bounds__(kCountThreads) bucket_count_kernel(const int32_t* __restrict__ indices,
                                                                      const int32_t* __restrict__ offsets, int32_t B,
                                                                      int shift, int nb, int32_t* __restrict__ hist,
                                                                      int32_t* __restrict__ queue_count) {
-  __shared__ int32_t sh[kMaxBuckets];
+  __shared__ int32_t sh[NBCAP];
   const int s = blockIdx.x, S = gridDim.x;
   const int64_t t = blockIdx.y;
   for (int i = threadIdx.x; i < nb; i += kCountThreads) sh[i] = 0;
@@ -156,25 +161,31 @@ __device__ __forceinline__ int count_not_above(int32_t ends, int32_t p) {
   return c;
 }
 
-// A CTA moves its slice in steps of kScatterTile pairs.  Every warp owns a contiguous share of the
+// A CTA moves its slice in steps of TILE pairs.  Every warp owns a contiguous share of the
 // slice and contributes its next 32 * kRounds positions to each step (walking one contiguous range
 // keeps the search for the bag of a position a matter of a few shuffles).  Per step: count the
 // buckets (the old value of a pair's counter is its slot among the step's pairs of that bucket),
 // gather the pairs bucket by bucket in shared memory, then copy them out: a bucket's share of the
 // step is one contiguous run of 8-byte pairs, so the stores coalesce instead of costing a sector per
 // pair.  Where a slice's pairs go inside a bucket follows from the histograms alone: slices in order.
-__global__ void __launch_bounds__(kScatterThreads, 3) bucket_scatter_kernel(
+//
+// NBCAP buckets per table fit the CTA's shared arrays and TILE pairs are gathered per step: (1024, 2048)
+// for the usual sparse batches, (4096, 4096) in dynamic shared memory for busy tables, where a step
+// still has to give every bucket more than a pair or two for the copy-out to coalesce.
+template <int NBCAP, int TILE>
+__global__ void __launch_bounds__(kScatterThreads, NBCAP <= kFewBuckets ? 3 : 2) bucket_scatter_kernel(
     const int32_t* __restrict__ indices, const int32_t* __restrict__ offsets, int32_t B, int64_t T, int idx_bits,
     int shift, int nb, const int32_t* __restrict__ hist, int32_t* __restrict__ bucket_start,
     uint2* __restrict__ pairs) {
-  __shared__ uint2 stage[kScatterTile];
-  __shared__ int32_t cnt[kMaxBuckets];     // pairs of the step per bucket, then their first slot in `stage`
-  __shared__ int32_t delta[kMaxBuckets];   // global position minus slot in `stage`, per bucket
-  __shared__ int32_t cursor[kMaxBuckets];  // next free global position of this slice in every bucket
+  extern __shared__ uint2 scatter_smem[];
+  uint2* stage = scatter_smem;                                     // TILE pairs
+  int32_t* cnt = reinterpret_cast<int32_t*>(scatter_smem + TILE);  // pairs of the step per bucket, then their first slot in `stage`
+  int32_t* delta = cnt + NBCAP;                                    // global position minus slot in `stage`, per bucket
+  int32_t* cursor = delta + NBCAP;                                 // next free global position of this slice in every bucket
   __shared__ int32_t warp_tot[kScatterThreads / 32];
   __shared__ int32_t step_total;
-  constexpr int kPer = kMaxBuckets / kScatterThreads;  // buckets per thread
-  constexpr int kRounds = kScatterTile / kScatterThreads;
+  constexpr int kPer = NBCAP / kScatterThreads;  // buckets per thread
+  constexpr int kRounds = TILE / kScatterThreads;
   constexpr int kWarps = kScatterThreads / 32;
 
   const int s = blockIdx.x, S = gridDim.x;
@@ -243,7 +254,7 @@ __global__ void __launch_bounds__(kScatterThreads, 3) bucket_scatter_kernel(
       key[r] = key_hi | static_cast<uint32_t>(index[r]);
       if (valid) {
         const uint32_t bk = bucket_of(index[r], shift, nb);
-        slot[r] = bk | (static_cast<uint32_t>(atomicAdd(&cnt[bk], 1)) << 10);
+        slot[r] = bk | (static_cast<uint32_t>(atomicAdd(&cnt[bk], 1)) << kBucketIdBits);
       }
       const int32_t pn = p + 32 * kRounds;  // the next step's index, in flight during this one
       index[r] = pn < cb ? __ldg(indices + pn) : 0;
@@ -320,7 +331,7 @@ __global__ void __launch_bounds__(kScatterThreads, 3) bucket_scatter_kernel(
 #pragma unroll
     for (int r = 0; r < kRounds; ++r)
       if (wa + r * 32 + lane < cb)
-        stage[cnt[slot[r] & 1023u] + (slot[r] >> 10)] = make_uint2(key[r], static_cast<uint32_t>(bagv[r]));
+        stage[cnt[slot[r] & (kMaxBuckets - 1)] + (slot[r] >> kBucketIdBits)] = make_uint2(key[r], static_cast<uint32_t>(bagv[r]));
     __syncthreads();
     for (int i = threadIdx.x; i < nb; i += kScatterThreads) cnt[i] = 0;
     const int32_t m = step_total;
@@ -628,11 +639,12 @@ bool bucket_geometry(int64_t T, int64_t N, int64_t max_rows_per_table, KeyLayout
   while (shift > 0 && avg * static_cast<double>(1ll << shift) / static_cast<double>(max_rows_per_table) > target)
     --shift;
   const int64_t nb = ((max_rows_per_table - 1) >> shift) + 1;
-  if (nb > kMaxBuckets) return false;  // tables too large (or too busy) for 1024 buckets of 2^14 rows
+  if (nb > kMaxBuckets) return false;  // tables too large (or too busy) for 4096 buckets of up to 2^14 rows
   g->shift = shift;
   g->nb = static_cast<int>(nb);
   const int64_t want = static_cast<int64_t>(avg / 8192.0) + 1;
-  const int64_t room = 3ll * device_sm_count() / T;  // the (slice, table) grid should be resident at once
+  // the (slice, table) grid should be resident at once: 3 CTAs of the narrow scatter variant fit an SM, 2 of the wide
+  const int64_t room = (nb > kFewBuckets ? 2ll : 3ll) * device_sm_count() / T;
   int64_t S = want < room ? want : room;
   if (S < 1) S = 1;
   if (S > 65535 || T > 65535) return false;
@@ -660,17 +672,35 @@ int bucket_sort_plan(const int32_t* indices, const int32_t* offsets, int64_t T, 
                                           kBucketSortCapacity * 8));
     opted_in[dev].store(true, std::memory_order_release);
   }
+  const bool wide = g.nb > kFewBuckets;
+  constexpr size_t kScatterSmem = kScatterTile * sizeof(uint2) + 3 * kFewBuckets * sizeof(int32_t);
+  constexpr size_t kScatterSmemWide = kScatterTileWide * sizeof(uint2) + 3 * kMaxBuckets * sizeof(int32_t);
+  static std::atomic<bool> wide_opted_in[64];
+  if (wide && dev < 64 && !wide_opted_in[dev].load(std::memory_order_acquire)) {
+    TBE_CUDA_TRY(cudaFuncSetAttribute(bucket_scatter_kernel<kMaxBuckets, kScatterTileWide>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kScatterSmemWide)));
+    wide_opted_in[dev].store(true, std::memory_order_release);
+  }
   {
     KernelTimer timer("bucket_count_kernel", stream);
-    bucket_count_kernel<<<grid, kCountThreads, 0, stream>>>(indices, offsets, static_cast<int32_t>(B), g.shift, g.nb,
-                                                            ws.hist, queue_count);
+    if (wide) {
+      bucket_count_kernel<kMaxBuckets><<<grid, kCountThreads, 0, stream>>>(indices, offsets, static_cast<int32_t>(B),
+                                                                          g.shift, g.nb, ws.hist, queue_count);
+    } else {
+      bucket_count_kernel<kFewBuckets><<<grid, kCountThreads, 0, stream>>>(indices, offsets, static_cast<int32_t>(B),
+                                                                          g.shift, g.nb, ws.hist, queue_count);
+    }
   }
   TBE_CHECK_LAUNCH("bucket_count_kernel");
   {
     KernelTimer timer("bucket_scatter_kernel", stream);
-    bucket_scatter_kernel<<<grid, kScatterThreads, 0, stream>>>(indices, offsets, static_cast<int32_t>(B), T,
-                                                                layout.idx_bits, g.shift, g.nb, ws.hist,
-                                                                ws.bucket_start, pairs);
+    if (wide) {
+      bucket_scatter_kernel<kMaxBuckets, kScatterTileWide><<<grid, kScatterThreads, kScatterSmemWide, stream>>>(
+          indices, offsets, static_cast<int32_t>(B), T, layout.idx_bits, g.shift, g.nb, ws.hist, ws.bucket_start, pairs);
+    } else {
+      bucket_scatter_kernel<kFewBuckets, kScatterTile><<<grid, kScatterThreads, kScatterSmem, stream>>>(
+          indices, offsets, static_cast<int32_t>(B), T, layout.idx_bits, g.shift, g.nb, ws.hist, ws.bucket_start, pairs);
+    }
   }
   TBE_CHECK_LAUNCH("bucket_scatter_kernel");
   {

@@ -6,11 +6,20 @@ slice of all tables, ``[B/W, T, D]`` -- the wiring of the reference's
 (sparse_embedding_cuda.cpp:471-533):  ``out_j[b', r*T/W + t] = in_r[j*B/W + b', t]``.
 
 Two exchanges:
-  * ``exchange="fused"`` -- no separate collective.  The forward kernel stores each pooled row
+  * ``exchange="fused"`` -- no collective call at all.  The forward kernel stores each pooled row
     straight into the owner rank's ``[B/W, T, D]`` buffer through peer-mapped (symmetric) memory,
     and the backward scatters the local gradient slice to the table owners with one peer-store
-    kernel; a stream-ordered NCCL barrier (a one-element all-reduce) separates producers from
-    consumers.  Neither direction needs a transpose copy.
+    kernel.  Producers and consumers are ordered by step-numbered flags in peer-mapped memory
+    (``tbe_peer_signal_wait``: a release store per peer, a bounded acquire poll per peer), and the
+    buffers are double-buffered: before a rank overwrites a peer's buffer it has seen that peer's
+    "free" flag, which the peer raises when its stream has passed every consumer of the buffer's
+    previous contents.  Neither direction needs a transpose copy.
+
+    Contract of the fused mode: ``forward`` returns a view of an exchange buffer.  It stays valid
+    until this rank launches its SECOND-next forward; work that reads it must be enqueued on the
+    stream ``forward`` ran on (or be ordered after it by events) before that launch.  Keep a
+    ``.clone()`` for anything longer-lived.  A wait that runs out (a peer died or never joined) is
+    reported by :meth:`TableShardedEmbeddingBags.check_exchange`, never by a hung GPU.
   * ``exchange="nccl"`` -- ``all_to_all_single`` plus the reference's transpose copies; this is the
     baseline the fused path is measured against, and the only mode that runs on CPU tensors (gloo),
     where it serves the host-logic tests.
@@ -64,26 +73,59 @@ class _NcclExchange(torch.autograd.Function):
         return pooled_all_to_all_backward(grad.contiguous(), ctx.group), None
 
 
-class _SymmetricBuffers:
-    """Peer-mapped buffers of one sharded module: the exchanged outputs and incoming gradients."""
+# rows of the flag matrix every rank owns (one 128-byte line each; slot j of a row is written by rank j)
+_OUT_FREE, _OUT_READY, _GRAD_FREE, _GRAD_READY = range(4)
+_FLAG_ROW_INTS = 32
 
-    def __init__(self, B, T_local, D, dtype, device, group):
+
+class _SymmetricBuffers:
+    """Peer-mapped state of one sharded module: two exchanged-output buffers, two incoming-gradient
+    buffers (alternating by step) and the flag matrix that orders their use across ranks."""
+
+    def __init__(self, B, T_local, D, dtype, device, group, timeout_s):
         import torch.distributed._symmetric_memory as symm_mem
         W = dist.get_world_size(group)
-        self.world, self.rank = W, dist.get_rank(group)
-        self.out = symm_mem.empty((B // W, T_local * W, D), dtype=dtype, device=device)
-        self.grad_in = symm_mem.empty((B, T_local, D), dtype=dtype, device=device)
-        self.out_handle = symm_mem.rendezvous(self.out, group=group)
-        self.grad_handle = symm_mem.rendezvous(self.grad_in, group=group)
+        assert W <= _lib.TBE_MAX_PEERS
+        self.world, self.rank, self.group = W, dist.get_rank(group), group
         ptr_array = ctypes.c_void_p * W
-        self.out_ptrs = ptr_array(*[int(p) for p in self.out_handle.buffer_ptrs])
-        self.grad_ptrs = ptr_array(*[int(p) for p in self.grad_handle.buffer_ptrs])
-        self._flag = torch.zeros(1, dtype=torch.float32, device=device)
-        self.group = group
 
-    def barrier(self):
-        # stream-ordered: completes on the device once every rank's preceding kernels have finished
-        dist.all_reduce(self._flag, group=self.group)
+        def shared(shape, dt):
+            t = symm_mem.empty(shape, dtype=dt, device=device)
+            handle = symm_mem.rendezvous(t, group=group)
+            return t, handle, [int(p) for p in handle.buffer_ptrs]
+
+        self.out, self.out_ptrs, self.grad_in, self.grad_ptrs, self._handles = [], [], [], [], []
+        for _ in range(2):
+            t, h, ptrs = shared((B // W, T_local * W, D), dtype)
+            self.out.append(t)
+            self.out_ptrs.append(ptr_array(*ptrs))
+            self._handles.append(h)
+            t, h, ptrs = shared((B, T_local, D), dtype)
+            self.grad_in.append(t)
+            self.grad_ptrs.append(ptr_array(*ptrs))
+            self._handles.append(h)
+        self.flags, h, ptrs = shared((4, _FLAG_ROW_INTS), torch.int32)
+        self._handles.append(h)
+        self.flag_ptrs = [ptr_array(*[p + 4 * _FLAG_ROW_INTS * row for p in ptrs]) for row in range(4)]
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.timeout_ns = int(timeout_s * 1e9)
+        self.fwd_step = 0
+        self.bwd_step = 0
+        self.plan_workspace = None
+        # nobody may signal before every rank has zeroed its flags
+        self.flags.zero_()
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+
+    def sync(self, row, signal_value, wait_value, stream):
+        """Raise this rank's slot of flag ``row`` on every peer to ``signal_value``, then wait (on the
+        device, bounded) until every peer's slot here has reached ``wait_value``."""
+        _lib.call("tbe_peer_signal_wait", self.flag_ptrs[row], self.flags[row].data_ptr(), self.world, self.rank,
+                  signal_value, wait_value, self.timeout_ns, self.status.data_ptr(), stream)
+
+    def check(self, stream):
+        host = (ctypes.c_int32 * 4)()
+        _lib.call("tbe_peer_status", self.status.data_ptr(), host, stream)
 
 
 class _FusedShardedLookup(torch.autograd.Function):
@@ -92,15 +134,20 @@ class _FusedShardedLookup(torch.autograd.Function):
         m = module
         buf = m._buffers_for(indices.device)
         T, B, D = m.local_tables, m.global_batch, m.embedding_dim
+        buf.fwd_step += 1
+        k, slot = buf.fwd_step, buf.fwd_step & 1
         with torch.cuda.device(weights.device):
+            stream = tbe_ext._stream(weights.device)
+            # my other output buffer is free from here on (its consumers precede this launch in stream
+            # order); the peers' buffers `slot` were declared free one step ago
+            buf.sync(_OUT_FREE, k, k - 1, stream)
             _lib.call("tbe_forward_sharded", weights.data_ptr(), m.tbe.table_offsets.data_ptr(), indices.data_ptr(),
-                      offsets.data_ptr(), None, buf.out_ptrs, buf.world, T, B, D, T * buf.world, T * buf.rank,
-                      tbe_ext._DTYPES[weights.dtype], tbe_ext._POOLING[m.tbe.pooling_mode],
-                      tbe_ext._stream(weights.device))
-            buf.barrier()
+                      offsets.data_ptr(), None, buf.out_ptrs[slot], buf.world, T, B, D, T * buf.world, T * buf.rank,
+                      tbe_ext._DTYPES[weights.dtype], tbe_ext._POOLING[m.tbe.pooling_mode], stream)
+            buf.sync(_OUT_READY, k, k, stream)
         ctx.module = m
         ctx.save_for_backward(weights, indices, offsets)
-        return buf.out.view(buf.out.shape)
+        return buf.out[slot].view(buf.out[slot].shape)
 
     @staticmethod
     def backward(ctx, grad):
@@ -109,15 +156,23 @@ class _FusedShardedLookup(torch.autograd.Function):
         buf = m._buffers_for(indices.device)
         T, B, D = m.local_tables, m.global_batch, m.embedding_dim
         grad = grad.contiguous()
+        buf.bwd_step += 1
+        k, slot = buf.bwd_step, buf.bwd_step & 1
         # the sort of the lookups needs no gradient: it runs on a side stream under the exchange
         plan = None
         if m.tbe.optimizer in (Optimizer.SGD, Optimizer.EXACT_ROWWISE_ADAGRAD):
-            plan = tbe_ext.backward_plan(m.tbe.table_offsets, indices, offsets, weights.size(0))
+            need = tbe_ext._workspace_bytes(indices.numel(), weights.size(0))
+            if buf.plan_workspace is None or buf.plan_workspace.numel() < need:
+                buf.plan_workspace = torch.empty(int(need * 1.1) + 4096, dtype=torch.uint8, device=weights.device)
+            plan = tbe_ext.backward_plan(m.tbe.table_offsets, indices, offsets, weights.size(0),
+                                         workspace=buf.plan_workspace)
         with torch.cuda.device(weights.device):
-            _lib.call("tbe_all2all_push", grad.data_ptr(), buf.grad_ptrs, buf.world, buf.rank, B // buf.world,
-                      T * D * grad.element_size(), tbe_ext._stream(weights.device))
-            buf.barrier()
-        m.apply_local_backward(buf.grad_in, indices, offsets, plan=plan)
+            stream = tbe_ext._stream(weights.device)
+            buf.sync(_GRAD_FREE, k, k - 1, stream)
+            _lib.call("tbe_all2all_push", grad.data_ptr(), buf.grad_ptrs[slot], buf.world, buf.rank, B // buf.world,
+                      T * D * grad.element_size(), stream)
+            buf.sync(_GRAD_READY, k, k, stream)
+        m.apply_local_backward(buf.grad_in[slot], indices, offsets, plan=plan)
         return None, None, None, None
 
 
@@ -126,7 +181,8 @@ class TableShardedEmbeddingBags(nn.Module):
     indices/offsets over the global batch and returns this rank's ``[B/W, T_total, D]`` slice."""
 
     def __init__(self, tables_per_rank, num_embeddings, embedding_dim, global_batch, optimizer=Optimizer.SGD,
-                 learning_rate=0.01, eps=None, fp16=False, pooling_mode="sum", exchange="fused", group=None):
+                 learning_rate=0.01, eps=None, fp16=False, pooling_mode="sum", exchange="fused", group=None,
+                 sync_timeout_s=30.0):
         super().__init__()
         assert exchange in ("fused", "nccl")
         self.group = group
@@ -136,6 +192,7 @@ class TableShardedEmbeddingBags(nn.Module):
         self.embedding_dim = embedding_dim
         self.global_batch = global_batch
         self.exchange = exchange
+        self.sync_timeout_s = sync_timeout_s
         self.tbe = TableBatchedEmbeddingBags(tables_per_rank, num_embeddings, embedding_dim, optimizer=optimizer,
                                              learning_rate=learning_rate, eps=eps, fp16=fp16,
                                              pooling_mode=pooling_mode)
@@ -145,8 +202,18 @@ class TableShardedEmbeddingBags(nn.Module):
         if self._symm is None:
             w = self.tbe.embedding_weights
             self._symm = _SymmetricBuffers(self.global_batch, self.local_tables, self.embedding_dim, w.dtype, device,
-                                           self.group if self.group is not None else dist.group.WORLD)
+                                           self.group if self.group is not None else dist.group.WORLD,
+                                           self.sync_timeout_s)
         return self._symm
+
+    def check_exchange(self):
+        """Synchronises the current stream and raises ``TBEError`` (status ``TBE_ERR_TIMEOUT``) if a
+        bounded device-side wait of the fused exchange ran out since the module was built -- the
+        results of the steps after it are then not to be trusted."""
+        if self._symm is not None:
+            dev = self.tbe.embedding_weights.device
+            with torch.cuda.device(dev):
+                self._symm.check(tbe_ext._stream(dev))
 
     def apply_local_backward(self, grad_local, indices, offsets, plan=None):
         """Fused backward + optimizer of the local tables for ``grad_local = [B, T/W, D]``; ``plan`` is

@@ -124,21 +124,22 @@ def _backward_workspace(weights, N, total_rows):
     return _workspace(weights.device, _workspace_bytes(N, total_rows))
 
 
-_max_rows_cache = {}  # (data_ptr, numel, version, total_rows) -> largest table
-
-
 def _max_rows_per_table(table_offsets, total_rows):
     """Row count of the largest table (lets the sort skip the table bits).  Reads ``table_offsets``
-    back once per distinct tensor -- a host synchronisation on the first call only."""
-    key = (table_offsets.data_ptr(), table_offsets.numel(), table_offsets._version, int(total_rows))
-    v = _max_rows_cache.get(key)
-    if v is None:
-        offs = table_offsets.detach().cpu().tolist() + [int(total_rows)]
-        diffs = [b - a for a, b in zip(offs[:-1], offs[1:])]
-        v = max(diffs) if diffs and min(diffs) >= 0 else 0
-        if len(_max_rows_cache) > 256:
-            _max_rows_cache.clear()
-        _max_rows_cache[key] = v
+    back once per tensor OBJECT and version -- a host synchronisation on the first call only.  The
+    value is kept on the tensor itself: an address can be handed to another tensor by the allocator,
+    an attribute cannot."""
+    cached = getattr(table_offsets, "_tbe_max_rows", None)
+    key = (table_offsets._version, int(total_rows), table_offsets.numel())
+    if cached is not None and cached[0] == key:
+        return cached[1]
+    offs = table_offsets.detach().cpu().tolist() + [int(total_rows)]
+    diffs = [b - a for a, b in zip(offs[:-1], offs[1:])]
+    v = max(diffs) if diffs and min(diffs) >= 0 else 0
+    try:
+        table_offsets._tbe_max_rows = (key, v)
+    except AttributeError:  # a tensor subclass without a __dict__
+        pass
     return v
 
 
@@ -161,10 +162,13 @@ class BackwardPlan:
         self.N, self.total_rows, self.max_rows = N, total_rows, max_rows
 
 
-def backward_plan(table_offsets, indices, offsets, total_rows):
+def backward_plan(table_offsets, indices, offsets, total_rows, workspace=None):
     """Starts sorting the lookups of ``(indices, offsets)`` on a side stream and returns a
     :class:`BackwardPlan`; pass it as ``plan=`` to a ``backward_*`` call for the same inputs.
-    Nothing here depends on the gradient, so it overlaps with the forward or with an exchange."""
+    Nothing here depends on the gradient, so it overlaps with the forward or with an exchange.
+    ``workspace`` (a uint8 CUDA tensor of at least ``tbe_backward_workspace_bytes``) lets a caller
+    that builds one plan per step reuse one buffer: the side stream first waits for everything
+    already enqueued on the current stream, which includes the backward that last read the buffer."""
     _check_cuda("table_offsets", table_offsets, torch.int32)
     _check_cuda("indices", indices, torch.int32)
     _check_cuda("offsets", offsets, torch.int32)
@@ -175,8 +179,17 @@ def backward_plan(table_offsets, indices, offsets, total_rows):
     max_rows = _max_rows_per_table(table_offsets, total_rows)
     with torch.cuda.device(dev):
         main, side = torch.cuda.current_stream(dev), _side_stream(dev)
-        ws = torch.empty(_workspace_bytes(N, total_rows), dtype=torch.uint8, device=dev)
-        ws.record_stream(side)
+        nbytes = _workspace_bytes(N, total_rows)
+        if workspace is None:
+            ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        else:
+            _require(workspace.is_cuda and workspace.dtype == torch.uint8 and workspace.numel() >= nbytes,
+                     "workspace must be a uint8 CUDA tensor of at least %d bytes" % nbytes)
+            ws = workspace
+        # the side stream reads tensors that were allocated on the main stream: tell the allocator,
+        # so that dropping the autograd graph without a backward cannot recycle them under the sort
+        for t in (ws, indices, offsets, table_offsets):
+            t.record_stream(side)
         side.wait_stream(main)
         _lib.call("tbe_backward_plan", table_offsets.data_ptr(), indices.data_ptr(), offsets.data_ptr(), T, B, N,
                   total_rows, max_rows, ws.data_ptr(), ws.numel(), ctypes.c_void_p(side.cuda_stream))

@@ -76,8 +76,10 @@ def _table_sort_case(rng, T, E, B, Lmax, hot):
     (70, 300000, 64, 30, False),       # more tables than one slice each can fill
     (1, 2 ** 20, 3000, 50, False),
     (3, 2 ** 20 + 1, 1500, 50, True),  # index bits roll over to 21
-    (1, 2 ** 24, 4096, 20, False),     # 1024 buckets of 2^14 rows: the most the two-level sort takes
-    (1, 2 ** 24 + 1, 4096, 20, False), # one more row: falls back to the device radix sort
+    (1, 2 ** 24, 4096, 20, False),     # 1024 buckets of 2^14 rows: the most the narrow kernel variants take
+    (1, 2 ** 24 + 1, 4096, 20, False), # one more row: the wide variants (up to 4096 buckets per table)
+    (1, 2 ** 26 + 1, 4096, 20, False), # more than 4096 buckets: falls back to the device radix sort
+    (2, 2 ** 20, 16384, 240, False),   # ~1.6 lookups per row: 2048 buckets of 512 rows, the wide variants
     (300, 5000, 8, 12, False),         # more tables than resident CTAs: one slice per table
 ])
 def test_table_segmented_sort_exact(cuda_device, T, E, B, Lmax, hot):
@@ -101,12 +103,13 @@ def test_table_segmented_sort_exact(cuda_device, T, E, B, Lmax, hot):
         assert np.array_equal(starts.cpu().numpy(), s0), sort_mode
 
 
-@pytest.mark.parametrize("bucket", [64, 300, 2048])
-def test_table_segmented_sort_bucket_sizes(cuda_device, bucket):
-    """The bucket-size knob changes the geometry (buckets per table, CTA variants), never the result."""
+@pytest.mark.parametrize("bucket,hot", [(8, False), (8, True), (64, False), (300, False), (2048, False)])
+def test_table_segmented_sort_bucket_sizes(cuda_device, bucket, hot):
+    """The bucket-size knob changes the geometry (buckets per table, CTA variants: 8 pairs per bucket
+    means 1563 buckets per table, the wide variants), never the result."""
     rng = np.random.default_rng(bucket)
     T, E, B = 4, 50000, 1024
-    indices, offsets = _table_sort_case(rng, T, E, B, 24, False)
+    indices, offsets = _table_sort_case(rng, T, E, B, 24, hot)
     dev = cuda_device
     to_np = np.arange(T, dtype=np.int64) * E
     to = torch.from_numpy(to_np.astype(np.int32)).to(dev)

@@ -65,6 +65,30 @@ def _worker(rank, world, port, exchange, dtype_name, failures):
             out.backward(grads[rank].to(dev))
             torch.cuda.synchronize()
             torch.testing.assert_close(m.tbe.embedding_weights.detach().float().cpu(), expect_w.float(), **tol)
+        # Two forwards in a row (an evaluation loop, or micro-batches before a backward): the first
+        # output must still hold when the second has been produced -- peers write the other buffer --
+        # and two backwards in a row must each see their own incoming gradient.
+        cases2 = [_rank_case(100 + r, Tl, E, D, B, Lmax, dtype) for r in range(world)]
+        local2 = [oracle.forward(w0_, to, i, o, compute_dtype=torch.float32) for (i, o, _), (_, _, w0_) in zip(cases2, cases)]
+        expect_out2 = oracle.all_to_all_pooled(local2)[rank]
+        idx2_d, off2_d = torch.from_numpy(cases2[rank][0]).to(dev), torch.from_numpy(cases2[rank][1]).to(dev)
+        m.tbe.embedding_weights.data.copy_(w0.to(dev))
+        out1 = m(idx_d, off_d)
+        out2 = m(idx2_d, off2_d)
+        torch.cuda.synchronize()
+        dist.barrier()  # every rank's second forward has landed
+        torch.testing.assert_close(out1.detach().float().cpu(), expect_out.float(), **tol)
+        torch.testing.assert_close(out2.detach().float().cpu(), expect_out2.float(), **tol)
+        out2.backward(grads[rank].to(dev))
+        out1.backward(grads[rank].to(dev))
+        torch.cuda.synchronize()
+        w_mid = oracle.sgd_step(w0, to, cases2[rank][0], cases2[rank][1], grad_in, lr, compute_dtype=torch.float32)
+        expect_w2 = oracle.sgd_step(w_mid, to, idx, off, grad_in, lr, compute_dtype=torch.float32)
+        torch.testing.assert_close(m.tbe.embedding_weights.detach().float().cpu(), expect_w2.float(), **tol)
+        with torch.no_grad():  # forward-only loop
+            for _ in range(3):
+                o = m(idx_d, off_d)
+        m.check_exchange()
         if exchange == "nccl" and dtype_name == "fp32":
             # row-wise sharding collectives, after test_sparse_embedding_cuda.py:138-171: the same seed
             # on every rank regenerates every rank's tensor
@@ -108,3 +132,62 @@ def test_sharded_forward_backward(exchange, dtype_name):
     assert not hung, "a rank did not finish: %s" % msgs
     assert not msgs, msgs
     assert all(p.exitcode == 0 for p in procs)
+
+
+def _absent_rank_worker(rank, world, port, failures):
+    """Rank 1 stays away from the second forward (a failure made on the host: it simply does not
+    call).  Rank 0's bounded wait must run out and be reported by check_exchange; rank 1 keeps its
+    process and buffers alive until rank 0 is done, so nothing ever touches freed peer memory."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    host_group = dist.new_group(backend="gloo")  # the ranks meet on the host at the end
+    try:
+        from sparse_ads_baselines_b200 import _lib
+        from sparse_ads_baselines_b200.sharded import TableShardedEmbeddingBags
+        Tl, E, D, B = 2, 50, 32, 8
+        idx, off, _ = _rank_case(rank, Tl, E, D, B, 4, torch.float32)
+        idx_d, off_d = torch.from_numpy(idx).to(dev), torch.from_numpy(off).to(dev)
+        m = TableShardedEmbeddingBags(Tl, E, D, B, exchange="fused", sync_timeout_s=1.0).to(dev)
+        with torch.no_grad():
+            m(idx_d, off_d)
+            m.check_exchange()  # the first step completes on both ranks
+            if rank == 0:
+                m(idx_d, off_d)  # rank 1 never launches this step
+                try:
+                    m.check_exchange()
+                    failures.put("rank 0: the missing rank went unnoticed")
+                except _lib.TBEError as e:
+                    if e.status != -6 or "rank 1" not in str(e):
+                        failures.put("rank 0: unexpected error %r" % e)
+                assert torch.arange(4, device=dev).sum().item() == 6  # the context survived
+        dist.barrier(group=host_group)
+    except Exception as e:
+        failures.put("rank %d: %r" % (rank, e))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_absent_rank_is_reported_not_waited_for():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    ctx = mp.get_context("spawn")
+    failures = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_absent_rank_worker, args=(r, 2, port, failures)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=180)
+    hung = [p for p in procs if p.is_alive()]
+    for p in hung:
+        p.kill()
+    msgs = []
+    while not failures.empty():
+        msgs.append(failures.get())
+    assert not hung, "a rank did not finish: %s" % msgs
+    assert not msgs, msgs
