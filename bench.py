@@ -47,6 +47,49 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
+# ------------------------------------------------------------------ DRAM traffic from profiler captures
+TRAFFIC_TABLE = os.path.join(ROOT, "profiles", "ncu_dram_traffic.txt")
+CSRC = os.path.join(ROOT, "sparse_ads_baselines_b200", "csrc")
+
+
+def source_digest(filenames):
+    """First 12 hex digits of the SHA-256 over the named csrc files ('+'-separated), in order."""
+    import hashlib
+    h = hashlib.sha256()
+    try:
+        for name in filenames.split("+"):
+            with open(os.path.join(CSRC, name), "rb") as f:
+                h.update(f.read())
+    except OSError:
+        return None
+    return h.hexdigest()[:12]
+
+
+def measured_traffic(kernel, workload_name, lookups):
+    """DRAM bytes per launch of ``kernel`` scaled from a profiler capture, or (None, why).
+
+    The table lists, per kernel and captured workload, the lookups of the captured launch, its
+    dram__bytes_read/write, the workloads it may be scaled to (same rows, bags and lengths per table,
+    so traffic grows with the lookups), and a digest of the kernel's source file at capture time.  A
+    row whose digest no longer matches the source is stale and gives no figure."""
+    try:
+        with open(TRAFFIC_TABLE) as f:
+            rows = [ln.split() for ln in f if ln.strip() and not ln.startswith("#")]
+    except OSError:
+        return None, "no capture table"
+    why = "no capture of %s that scales to workload %s" % (kernel, workload_name)
+    for r in rows:
+        if len(r) < 9 or r[0] != kernel or workload_name not in r[5].split(","):
+            continue
+        if source_digest(r[6]) != r[7]:
+            why = "stale: %s changed since the capture of %s" % (r[6], r[8])
+            continue
+        per_lookup = (float(r[3]) + float(r[4])) / float(r[2])
+        return per_lookup * lookups, ("ncu dram__bytes_read.sum + dram__bytes_write.sum of %s on workload %s "
+                                      "(%s lookups per launch, captured %s), scaled by lookups" % (kernel, r[1], r[2], r[8]))
+    return None, why
+
+
 # ------------------------------------------------------------------ clocks
 _JSON_OUT = None
 
@@ -146,15 +189,15 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------ CPU reference path
-def cpu_reference_run(w, steps, warmup, budget_s=20.0):
+def cpu_reference_run(w, steps, warmup, budget_s=20.0, force_fp32=False):
     """Times the reference's CPU path -- one torch.nn.EmbeddingBag(sparse=True) per table, forward,
     backward, sparse SGD -- on a bounded sample of the workload: T_cpu tables of the same E, D, B, L
     and index distribution.  Lookups/s does not depend on how many independent tables are looped
     over, so the sample's rate stands for the workload's."""
     from oracle import tbe_oracle as oracle
     T_cpu = min(w.T, 4)
-    dtype = torch.float16 if w.dtype == "fp16" else torch.float32
-    note = ""
+    dtype = torch.float16 if (w.dtype == "fp16" and not force_fp32) else torch.float32
+    note = " (fp32 tables)" if force_fp32 and w.dtype == "fp16" else ""
     torch.set_num_threads(os.cpu_count() or 1)
     indices, offsets = workloads.make_inputs(w, T=T_cpu)
     offsets64 = offsets.astype(np.int64)
@@ -206,17 +249,41 @@ def run_reference(args, rank):
     if rank != 0:
         return
     w = workloads.WORKLOADS[args.workload]
-    base = cpu_reference_run(w, args.steps, args.warmup, budget_s=120.0)
+    base = cpu_reference_run(w, args.steps, args.warmup, budget_s=90.0)
+    N, U, nbags = workload_counts(w)
     line = {
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
         "steps": base["steps"], "warmup": args.warmup, "ms_per_step": base["ms_per_step"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
-        "config": {"workload": describe(w, args.gpus)},
+        "config": config_of(w, args.gpus, N * args.gpus, U, args.exchange if args.gpus > 1 else "none"),
         "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    if w.dtype == "fp16":  # the CPU kernels' fp16 path is slow; the same run on fp32 tables stands beside it
+        fp32 = cpu_reference_run(w, max(args.steps // 2, 2), 1, budget_s=30.0, force_fp32=True)
+        line["cpu_baseline"]["value_fp32_tables"] = fp32["value"]
     emit(line)
+
+
+def workload_counts(w):
+    """(mean lookups, mean distinct rows, bags) of rank 0's rotating batches, from the host generator."""
+    n = u = 0
+    for r in range(ROTATE):
+        idx, off = workloads.make_inputs(w, seed=w.seed + r)
+        n += int(idx.size)
+        u += workloads.count_unique_rows(idx, off, w.T, w.B, w.E)
+    return n / ROTATE, u / ROTATE, w.T * w.B
+
+
+def config_of(w, n_gpus, lookups_per_step, unique_rows_per_rank, exchange):
+    """The ``config`` object of the JSON line: the same keys on both arms."""
+    return {"workload": describe(w, n_gpus), "lookups_per_step": lookups_per_step,
+            "unique_rows_per_step": unique_rows_per_rank, "exchange": exchange,
+            "l2": "inputs larger than L2: %.1f GB of tables per GPU, %d rotating index batches"
+                  % (w.T * w.E * w.D * w.elem_bytes / 1e9, ROTATE),
+            "lookup_bytes_per_step_reference_convention": workloads.lookup_bytes(w, lookups_per_step / n_gpus,
+                                                                                w.optimizer != "none")}
 
 
 def describe(w, n_gpus):
@@ -236,21 +303,73 @@ def init_tables(module, w, seed):
         block.copy_(torch.rand(block.shape, device=data.device, generator=gen) * 0.02 - 0.01)
 
 
-def run_ours(args, rank, world, local_rank):
+def make_batches(w, rank, device, rotate):
+    """``rotate`` seeded index batches of one rank: host generator for the usual sizes, the device's
+    generator (same distribution: uniform rows, fixed bag length) for batches of 10^8 lookups."""
+    batches = []
+    big = w.T * w.B * max(w.L, 1) > 50_000_000
+    for r in range(rotate):
+        seed = w.seed + 1000 * rank + r
+        if big:
+            assert w.index_dist == "uniform" and w.L_dist == "fixed"
+            gen = torch.Generator(device=device).manual_seed(seed)
+            N = w.T * w.B * w.L
+            idx_d = torch.randint(0, w.E, (N,), device=device, dtype=torch.int32, generator=gen)
+            off_d = (torch.arange(w.T * w.B + 1, device=device, dtype=torch.int64) * w.L).to(torch.int32)
+            U = 0
+            per_table = w.B * w.L
+            for t in range(w.T):
+                U += int(torch.unique(idx_d[t * per_table:(t + 1) * per_table]).numel())
+            batches.append(dict(idx=idx_d, off=off_d, N=N, U=U, idx_h=None, off_h=None))
+            continue
+        idx, off = workloads.make_inputs(w, seed=seed)
+        idx_d, off_d = torch.from_numpy(idx).to(device), torch.from_numpy(off).to(device)
+        table_of_pos = torch.repeat_interleave(torch.arange(w.T * w.B, device=device) // w.B,
+                                               (off_d[1:] - off_d[:-1]).long())
+        U = int(torch.unique(table_of_pos * w.E + idx_d.long()).numel())
+        batches.append(dict(idx=idx_d, off=off_d, N=int(idx.size), U=U, idx_h=torch.from_numpy(idx).pin_memory(),
+                            off_h=torch.from_numpy(off).pin_memory()))
+        del table_of_pos
+    return batches
+
+
+def host_link_rates(device, world):
+    """Pinned-memory copy rates of this rank with every rank copying at once (GB/s, max-time over
+    ranks): what the host side of the end-to-end leg can deliver at most."""
+    import torch.distributed as dist
+    nbytes = 256 << 20
+    h = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    d = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    out = {}
+    for name, (dst, src) in (("h2d", (d, h)), ("d2h", (h, d))):
+        dst.copy_(src, non_blocking=True)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(8):
+            dst.copy_(src, non_blocking=True)
+        t1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([t0.elapsed_time(t1)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        out[name + "_gbs_per_rank"] = 8 * nbytes / (float(ms.item()) * 1e-3) / 1e9
+    out["note"] = "256 MiB pinned copies, all %d ranks at once, slowest rank" % world
+    return out
+
+
+def measure(args, w, rank, world, local_rank, rotate=ROTATE, with_e2e=True, with_cpu=True, regions=5):
+    """Runs workload ``w`` (``w.T`` tables on every rank, global batch ``w.B``) and returns rank 0's
+    JSON line as a dict (None on other ranks)."""
     import torch.distributed as dist
     from sparse_ads_baselines_b200 import _lib
     from sparse_ads_baselines_b200 import table_batched_embeddings as tbe
     from sparse_ads_baselines_b200 import table_batched_embeddings_ops as ops
     from sparse_ads_baselines_b200.sharded import TableShardedEmbeddingBags
 
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: there is no CPU path (use --impl reference for the CPU baseline)")
-    w = workloads.WORKLOADS[args.workload]
     device = torch.device("cuda", local_rank)
-    torch.cuda.set_device(device)
-    for pair in filter(None, args.tune.split(",")):
-        knob, val = pair.split("=")
-        _lib.call("tbe_set_tuning", knob.encode(), int(val))
     fp16 = w.dtype == "fp16"
     tdt = torch.float16 if fp16 else torch.float32
     opt = {"sgd": ops.Optimizer.SGD, "none": ops.Optimizer.SGD,
@@ -265,24 +384,15 @@ def run_ours(args, rank, world, local_rank):
     module.plan_ahead = bool(args.plan_ahead)
     init_tables(module, w, seed=1234 + rank)
 
-    # ROTATE distinct batches; every rank draws the global batch for its own tables
-    batches = []
-    for r in range(ROTATE):
-        idx, off = workloads.make_inputs(w, seed=w.seed + 1000 * rank + r)
-        idx_d, off_d = torch.from_numpy(idx).to(device), torch.from_numpy(off).to(device)
-        table_of_pos = torch.repeat_interleave(torch.arange(w.T * w.B, device=device) // w.B,
-                                               (off_d[1:] - off_d[:-1]).long())
-        U = int(torch.unique(table_of_pos * w.E + idx_d.long()).numel())
-        batches.append(dict(idx=idx_d, off=off_d, N=int(idx.size), U=U, idx_h=torch.from_numpy(idx).pin_memory(),
-                            off_h=torch.from_numpy(off).pin_memory()))
-        del table_of_pos
+    # `rotate` distinct batches; every rank draws the global batch for its own tables
+    batches = make_batches(w, rank, device, rotate)
     gen = torch.Generator(device=device).manual_seed(99 + rank)
     grad = torch.randn(Bl, w.T * world, w.D, device=device, generator=gen).to(tdt)  # upstream gradient, local slice
-    N = sum(b["N"] for b in batches) / ROTATE   # mean lookups per step (ragged workloads differ per batch)
+    N = sum(b["N"] for b in batches) / rotate   # mean lookups per step (ragged workloads differ per batch)
     nbags = w.T * w.B
 
     def step(i):
-        b = batches[i % ROTATE]
+        b = batches[i % rotate]
         if world == 1 and not backward:
             with torch.no_grad():
                 module(b["idx"], b["off"])
@@ -292,21 +402,25 @@ def run_ours(args, rank, world, local_rank):
             out.backward(grad)
 
     def timed(n_steps):
+        """(device ms, host ms) of n_steps: CUDA events around the region, max over ranks; the host
+        figure is the time the launching thread needed to enqueue the region."""
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
+        h0 = time.perf_counter()
         for i in range(n_steps):
             step(i)
+        h1 = time.perf_counter()
         stop.record()
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
-        ms = torch.tensor([start.elapsed_time(stop)], device=device)
+        ms = torch.tensor([start.elapsed_time(stop), (h1 - h0) * 1e3], device=device)
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
+        return float(ms[0].item()), float(ms[1].item())
 
     with ClockSampler(local_rank) as clocks:
         for i in range(args.warmup):
@@ -314,9 +428,15 @@ def run_ours(args, rank, world, local_rank):
         launches0 = _lib.lib().tbe_kernel_launch_count()
         torch.cuda.synchronize()
         clocks.open_window()
-        total_ms = timed(args.steps)
-        launches = _lib.lib().tbe_kernel_launch_count() - launches0
-        ms_per_step = total_ms / args.steps
+        # the region of `steps` steps is timed `regions` times back to back; the line reports the median
+        region_ms, host_ms = [], []
+        for r in range(regions):
+            d_ms, h_ms = timed(args.steps)
+            region_ms.append(d_ms / args.steps)
+            host_ms.append(h_ms / args.steps)
+            if r == 0:
+                launches = _lib.lib().tbe_kernel_launch_count() - launches0
+        ms_per_step = statistics.median(region_ms)
         # keep the same load on, untimed, until the clock sampler has had 1.5 s of it (every rank runs
         # the same number of steps: ms_per_step is the maximum over ranks)
         extra = torch.tensor([clocks.extra_steps(ms_per_step)], device=device)
@@ -326,73 +446,114 @@ def run_ours(args, rank, world, local_rank):
             step(i)
         torch.cuda.synchronize()
         clocks.close_window()
+    sharded.check_exchange()
     value = N * world / (ms_per_step * 1e-3)
 
-    # second, identical pass with per-launch events for the per-kernel breakdown
+    # one more identical region with per-launch events for the per-kernel breakdown
     _lib.kernel_timing_enable(True)
     timed(args.steps)
     kt = _lib.kernel_timing_read()
     _lib.kernel_timing_enable(False)
 
     peak, peak_kind = measured_peaks()
-    U_mean = sum(b["U"] for b in batches) / ROTATE
+    U_mean = sum(b["U"] for b in batches) / rotate
     alg = workloads.algorithmic_bytes(w, N, U_mean, nbags, backward)
     kernel_bytes = {"tbe_forward_kernel": alg["fwd"], "run_kernel": alg["bwd"]}
-    # DRAM bytes per lookup of the two big kernels from the ncu capture of the `prof` workload that is
-    # summarised under profiles/: a quarter of the target's tables with the same rows, bags and
-    # lengths per table, so traffic grows with the lookups.  Only workloads of that per-table shape
-    # get a figure.
-    measured_traffic_per_lookup = {"run_kernel": 462.98, "tbe_forward_kernel": 255.02}
-    same_shape_as_prof = (w.E, w.D, w.B, w.L, w.dtype, w.index_dist, w.L_dist) == (1_000_000, 128, 2048, 38, "fp16",
-                                                                                   "uniform", "fixed")
     top = max((k for k in kt if k in kernel_bytes), key=lambda k: kt[k][1])
     top_ms = kt[top][1] / kt[top][0]
     achieved = kernel_bytes[top] / (top_ms * 1e-3) / 1e9
+    if args.traffic is not None:
+        traffic, traffic_source = args.traffic, "given on the command line"
+    else:
+        traffic, traffic_source = measured_traffic(top, w.name, N)
+    step_frac = alg["step"] / (ms_per_step * 1e-3) / 1e9 / peak
     roofline = {
         "bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-        "peak_kind": peak_kind,
-        "traffic": args.traffic if args.traffic is not None else
-        (measured_traffic_per_lookup[top] * N if same_shape_as_prof and world == 1 else None),
-        "traffic_source": "ncu dram__bytes_read+write of the prof workload (profiles/), scaled by lookups",
+        "peak_kind": peak_kind, "traffic": traffic, "traffic_source": traffic_source,
         "algorithmic_bytes_per_launch": kernel_bytes[top],
         "avg_launch_ms": top_ms,
         "step": {"algorithmic_bytes": alg["step"], "achieved": alg["step"] / (ms_per_step * 1e-3) / 1e9,
-                 "frac": alg["step"] / (ms_per_step * 1e-3) / 1e9 / peak,
-                 "frac_of_nominal_8TBs": alg["step"] / (ms_per_step * 1e-3) / 1e9 / 8000.0},
+                 "frac": step_frac, "frac_of_nominal_8TBs": alg["step"] / (ms_per_step * 1e-3) / 1e9 / 8000.0},
         "kernels_ms_per_step": {k: v[1] / args.steps for k, v in sorted(kt.items())},
     }
 
     # end to end with host buffers: through the extension functions at N = 1, through the sharded
     # module (exchange included) on several ranks
     e2e = None
-    if not args.no_e2e:
+    if with_e2e and not args.no_e2e and batches[0]["idx_h"] is not None:
         if world == 1:
             e2e = run_e2e(args, w, module, batches, grad, backward, tbe, device)
         else:
             e2e = run_e2e_sharded(args, w, sharded, batches, grad, backward, device, world)
+        e2e["host_link"] = host_link_rates(device, world)
+        per_rank_bytes = max(e2e["h2d_bytes_per_step"], e2e["d2h_bytes_per_step"]) / world
+        link = min(e2e["host_link"]["h2d_gbs_per_rank"], e2e["host_link"]["d2h_gbs_per_rank"])
+        e2e["host_link"]["ceiling_lookups_per_s"] = N * world / (per_rank_bytes / (link * 1e9))
 
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if with_cpu and rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_reference_run(w, steps=8, warmup=1, budget_s=20.0)
         cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
 
+    line = None
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong" if w.name == "cfg5" and world > 1 else "weak",
             "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
-            "config": {"workload": describe(w, world), "lookups_per_step": N * world, "unique_rows_per_step": U_mean,
-                       "exchange": args.exchange if world > 1 else "none",
-                       "l2": "inputs larger than L2: %.1f GB of tables per GPU, %d rotating index batches"
-                             % (w.T * w.E * w.D * w.elem_bytes / 1e9, ROTATE),
-                       "lookup_bytes_per_step_reference_convention": workloads.lookup_bytes(w, N, backward)},
-            "clocks": clocks.summary(), "roofline": roofline, "gpu_launches": int(launches),
-            "library_launches_note": "gpu_launches counts this library's own kernels; CUB sort/select launches are extra",
+            "config": config_of(w, world, N * world, U_mean, args.exchange if world > 1 else "none"),
+            "timing": {"regions": regions, "steps_per_region": args.steps, "ms_per_step_median": ms_per_step,
+                       "ms_per_step_min": min(region_ms), "ms_per_step_max": max(region_ms),
+                       "host_ms_per_step": statistics.median(host_ms),
+                       "note": "each region: CUDA events around `steps` steps, max over ranks; host_ms is the time "
+                               "the launching thread took to enqueue a step"},
+            "clocks": clocks.summary(), "roofline": roofline, "step_roofline_frac": step_frac,
+            "gpu_launches": int(launches),
+            "library_launches_note": "gpu_launches counts this library's own kernels in one timed region; CUB sort/select launches are extra",
         }
         if e2e is not None:
             line["e2e"] = e2e
         if cpu is not None:
             line["cpu_baseline"] = cpu
+    del sharded, module, batches, grad
+    tbe.release_workspaces()
+    torch.cuda.empty_cache()
+    return line
+
+
+def cfg5_workload(world):
+    """Config 5 at ``world`` ranks: 512 tables re-sharded 512/world per rank, global batch 65,536
+    (pytorch_distributed_benchmark.py:208-231).  One rank cannot hold all 512 tables plus the batch,
+    so ``world`` = 1 runs one rank's share of the 8-rank problem (64 tables)."""
+    import dataclasses
+    base = workloads.WORKLOADS["cfg5"]
+    return dataclasses.replace(base, T=(512 // world) if world > 1 else 64)
+
+
+def run_ours(args, rank, world, local_rank):
+    from sparse_ads_baselines_b200 import _lib
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path (use --impl reference for the CPU baseline)")
+    torch.cuda.set_device(torch.device("cuda", local_rank))
+    for pair in filter(None, args.tune.split(",")):
+        knob, val = pair.split("=")
+        _lib.call("tbe_set_tuning", knob.encode(), int(val))
+    if args.workload == "cfg5":
+        line = measure(args, cfg5_workload(world), rank, world, local_rank, rotate=2, with_e2e=False, regions=3)
+    else:
+        line = measure(args, workloads.WORKLOADS[args.workload], rank, world, local_rank)
+        if world > 1 and args.workload == "target" and not args.no_cfg5:
+            # the table-sharded configuration at its own shapes rides along on multi-GPU runs
+            saved = args.steps
+            args.steps = max(min(saved, 5), 2)
+            sub = measure(args, cfg5_workload(world), rank, world, local_rank, rotate=2, with_e2e=False, with_cpu=False,
+                          regions=3)
+            args.steps = saved
+            if line is not None:
+                line["cfg5"] = {k: sub[k] for k in ("value", "unit", "ms_per_step", "scaling", "config", "timing",
+                                                    "roofline", "steps", "gpu_launches")}
+    if rank == 0:
         emit(line)
 
 
@@ -629,6 +790,8 @@ def main():
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
+    ap.add_argument("--no-cfg5", action="store_true",
+                    help="multi-GPU runs of the target also time config 5 at its own shapes; this skips it")
     ap.add_argument("--plan-ahead", type=int, default=0,
                     help="1: sort the lookups for the backward on a side stream while the forward runs")
     ap.add_argument("--tune", default="", help="comma-separated knob=value pairs passed to tbe_set_tuning")

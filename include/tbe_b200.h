@@ -101,6 +101,17 @@ TBE_API int tbe_forward_strided(const void* weights, const int32_t* table_offset
                 const void* per_sample_weights, void* output, int64_t out_stride_b,
                 int64_t T, int64_t B, int64_t D, int dtype, int pooling, void* stream);
 
+/* Tables of different width in ONE launch: weights is a flat vector, table t's rows start at element
+ * weight_offsets[t] (int64 [T+1]) and are dim_offsets[t+1] - dim_offsets[t] wide (int32 [T+1]); the
+ * pooled rows go to columns [dim_offsets[t], dim_offsets[t+1]) of output [B][total_D].  Every width
+ * must be a multiple of 4; vector_bytes is 16 when every table's rows, and every table's output
+ * column block, start on 16-byte boundaries (always true for fp32), else 8 (fp16 only).  Sum pooling.
+ * replaces table_batched_embeddings_cuda.cu:882-1004 (batched_embedding_forward_mixed_D_cuda). */
+TBE_API int tbe_forward_mixed(const void* weights, const int64_t* weight_offsets, const int32_t* dim_offsets,
+                              const int32_t* indices, const int32_t* offsets, const void* per_sample_weights,
+                              void* output, int64_t T, int64_t B, int64_t total_D, int dtype, int vector_bytes,
+                              void* stream);
+
 /* Table-sharded forward with the all-to-all fused into the store: this rank owns
  * T local tables (global columns t0 .. t0+T of T_total) and looks up the GLOBAL
  * batch B for them; sample b belongs to rank b / (B / world) and its pooled row is
@@ -129,7 +140,22 @@ TBE_API int tbe_forward_sharded(const void* weights, const int32_t* table_offset
 TBE_API int tbe_all2all_push(const void* src, void* const* peer_dst, int world, int rank,
                              int64_t rows_local, int64_t chunk_bytes, void* stream);
 
-/* Ordering between ranks for the two exchange kernels above, without a collective: every rank owns a
+/* Row-wise sharding (every rank holds a slice of the rows of every table and looks up the global batch
+ * with indices local to its slice; the reference's UniformShardedEmbeddingBags + ReduceScatterFunction,
+ * models.py:194-209).  Forward: every rank stores its partial pooled rows for the samples of rank j
+ * into slot `rank` of rank j's buffer [world][B/world][T][D] -- that is tbe_forward_sharded with
+ * peer_outputs[j] advanced by rank slots, T_total = T and t0 = 0 -- and, once all slots have landed,
+ * rank j sums them:  out[i] = sum_r slots[r][i], r ascending, fp32 accumulation (fp64 for TBE_F64).
+ * replaces sparse_embedding_cuda.cpp:417-448 (forward_reduce_scatter: ncclReduceScatter). */
+TBE_API int tbe_reduce_slots(const void* slots, void* out, int world, int64_t elems_per_slot, int dtype,
+                             void* stream);
+/* Backward of the same: every rank's gradient slice [B/world][T][D] (`bytes` long) goes to slot `rank`
+ * of every peer's [world][B/world][T][D] = [B][T][D] buffer by direct peer stores.
+ * replaces sparse_embedding_cuda.cpp:535-566 (forward_allgather: ncclAllGather). */
+TBE_API int tbe_allgather_push(const void* src, void* const* peer_dst, int world, int rank, int64_t bytes,
+                               void* stream);
+
+/* Ordering between ranks for the exchange kernels above, without a collective: every rank owns a
  * flag array int32 [world] that all peers can write (peer-mapped, zero-initialised before first
  * use); rank r writes slot r of every peer's array.  One launch of one small CTA does, per peer j,
  *   signal: if peer_flags != NULL, store signal_value to peer_flags[j][rank] with release semantics at
@@ -273,6 +299,15 @@ TBE_API int tbe_sort_segments(const int32_t* table_offsets, const int32_t* indic
 TBE_API int tbe_construct_offsets(const int32_t* batch_offsets_per_table,
                           const int32_t* total_indices_per_table,
                           int32_t* lengths_out, int64_t T, int64_t B, void* stream);
+
+/* Ragged gather of bags: destination bag g = [dst_offsets[g], dst_offsets[g+1]) receives the indices of
+ * source bag src_bag[g] = [src_offsets[src_bag[g]], ...) (same length; the caller builds dst_offsets as
+ * the cumulative sum of the permuted lengths).  It is the last step of the index all-to-all that turns
+ * data-parallel sparse features ([T][B/W][L] per rank) into the table-sharded layout ([T/W][B][L]) the
+ * lookup consumes.  The reference fabricates table-sharded indices on every rank instead of exchanging
+ * them (pytorch_distributed_benchmark.py:227-231), so this has no counterpart to replace there. */
+TBE_API int tbe_permute_bags(const int32_t* src_indices, const int32_t* src_offsets, const int32_t* src_bag,
+                             const int32_t* dst_offsets, int32_t* dst_indices, int64_t nbags, void* stream);
 
 /* Validates indices/offsets on the device and SYNCHRONISES the stream: offsets[0]==0,
  * non-decreasing, offsets[T*B]==N, 0 <= index < rows of its table (rows_per_table

@@ -255,6 +255,51 @@ def all_to_all_pooled_backward(per_rank_grads):
     return outs
 
 
+def index_all_to_all(per_rank_indices, per_rank_offsets, num_tables):
+    """What the index all-to-all must deliver (no counterpart in the reference, which fabricates
+    table-sharded indices, pytorch_distributed_benchmark.py:227-231): rank j holds the features of its
+    batch slice for all T tables ([T][B/W] bags); rank r receives, for its tables
+    [r*T/W, (r+1)*T/W), bag (t, j*B/W + b') = rank j's bag (r*T/W + t, b').  Returns per rank
+    (indices, offsets) in [T/W][B] order.  Pure-Python loops: small cases only."""
+    W = len(per_rank_indices)
+    T = int(num_tables)
+    Tl = T // W
+    Bl = (len(per_rank_offsets[0]) - 1) // T
+    out = []
+    for r in range(W):
+        idx, lens = [], []
+        for t in range(Tl):
+            for j in range(W):
+                off = np.asarray(per_rank_offsets[j], dtype=np.int64)
+                for b in range(Bl):
+                    bag = (r * Tl + t) * Bl + b
+                    seg = np.asarray(per_rank_indices[j][off[bag]:off[bag + 1]])
+                    idx.append(seg)
+                    lens.append(len(seg))
+        indices = np.concatenate(idx).astype(np.int32) if idx else np.zeros(0, dtype=np.int32)
+        out.append((indices, np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)))
+    return out
+
+
+def reduce_scatter_pooled(per_rank_partials):
+    """Row-wise sharding, forward (forward_reducescatter, sparse_embedding_cuda.cpp:417-448, tested by
+    test_sparse_embedding_cuda.py:138-171): every rank holds partial pooled rows [B][T][D] for the
+    global batch; rank j receives the sum over ranks of rows [j*B/W, (j+1)*B/W)."""
+    W = len(per_rank_partials)
+    B = per_rank_partials[0].shape[0]
+    assert B % W == 0
+    Bl = B // W
+    total = torch.stack([torch.as_tensor(p).double() for p in per_rank_partials]).sum(0)
+    return [total[j * Bl:(j + 1) * Bl].to(torch.as_tensor(per_rank_partials[0]).dtype) for j in range(W)]
+
+
+def all_gather_pooled_backward(per_rank_grads):
+    """Backward of the reduce-scatter (forward_allgather, sparse_embedding_cuda.cpp:535-566): every rank
+    receives the concatenation over ranks of the gradient slices [B/W][T][D] -> [B][T][D]."""
+    full = torch.cat([torch.as_tensor(g) for g in per_rank_grads], dim=0)
+    return [full.clone() for _ in per_rank_grads]
+
+
 # ------------------------------------------------------------------ timed CPU baseline
 class PerTableEmbeddingBags:
     """The reference's CPU path for this workload: one ``nn.EmbeddingBag(sparse=True)`` per table,

@@ -27,9 +27,12 @@ SIGNATURES = {
     "tbe_kernel_timing_read": (_i64, [ctypes.c_char_p, _i64]),
     "tbe_forward": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
     "tbe_forward_strided": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _i32, _vp]),
+    "tbe_forward_mixed": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
     "tbe_forward_sharded": (_i32, [_vp, _vp, _vp, _vp, _vp, ctypes.POINTER(_vp), _i32, _i64, _i64, _i64, _i64,
                                    _i64, _i32, _i32, _vp]),
     "tbe_all2all_push": (_i32, [_vp, ctypes.POINTER(_vp), _i32, _i32, _i64, _i64, _vp]),
+    "tbe_reduce_slots": (_i32, [_vp, _vp, _i32, _i64, _i32, _vp]),
+    "tbe_allgather_push": (_i32, [_vp, ctypes.POINTER(_vp), _i32, _i32, _i64, _vp]),
     "tbe_peer_signal_wait": (_i32, [ctypes.POINTER(_vp), _vp, _i32, _i32, _i32, _i32, _i64, _vp, _vp]),
     "tbe_peer_status": (_i32, [_vp, ctypes.POINTER(ctypes.c_int32), _vp]),
     "tbe_backward_workspace_bytes": (_i64, [_i64, _i64]),
@@ -47,6 +50,7 @@ SIGNATURES = {
                                                    _vp, _i64, _vp]),
     "tbe_sort_segments": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
     "tbe_construct_offsets": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp]),
+    "tbe_permute_bags": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp]),
     "tbe_check_inputs": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "tbe_alloc_managed": (_i32, [ctypes.POINTER(_vp), _i64]),
     "tbe_free_managed": (_i32, [_vp]),

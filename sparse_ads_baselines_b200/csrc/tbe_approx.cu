@@ -6,6 +6,11 @@
 // rows race; here the lookups of one row are applied one after the other in ascending index
 // position, which is what the reference computes whenever no row repeats.
 //
+// Lookups without per-sample weights take approx_backward_sorted (tbe_backward.cu): the library's own
+// table-segmented sort, and runs reduced by lane groups with the per-lookup step sizes obtained from a
+// prefix sum (hot rows by a whole CTA).  Per-sample weights need every lookup's index position, which
+// that sort does not carry; they, and rows wider than 1 KB, take the path in this file:
+//
 //  1. prep kernel (a warp per bag): g2 = |grad[b][t]|^2 (times w_l^2 when weighted) stored per index
 //     position, sort key and position emitted for the sort, and for weighted lookups the gradient
 //     of the per-sample weight, <weights[row], grad[b][t]>, taken BEFORE any row is updated.
@@ -262,6 +267,13 @@ extern "C" int tbe_backward_approx_rowwise_adagrad(
   if (rc != TBE_OK) return rc;
   TBE_REQUIRE(D > 0 && D % 4 == 0, "%s: D must be a positive multiple of 4 (got %lld)", who, (long long)D);
   TBE_REQUIRE(dtype == TBE_F32 || dtype == TBE_F16 || dtype == TBE_F64, "%s: bad dtype %d", who, dtype);
+  if (!per_sample_weights) {
+    // unweighted lookups run on the table-segmented sort and the lane-group run kernels
+    rc = approx_backward_sorted(grad_output, stride_b, stride_t, weights, table_offsets, indices, offsets,
+                                optimizer_state, T, B, D, N, total_rows, dtype, lr, eps, stochastic_rounding, sr_seed,
+                                sr_offset, max_rows_per_table, workspace, workspace_bytes, stream_v);
+    if (rc != TBE_ERR_UNSUPPORTED) return rc;
+  }
   Workspace ws;
   rc = prepare_workspace(who, workspace, workspace_bytes, N, total_rows, &ws);
   if (rc != TBE_OK || N == 0) return rc;

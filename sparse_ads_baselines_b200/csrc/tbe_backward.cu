@@ -86,7 +86,7 @@ int carve(void* base, int64_t N, int64_t total_rows, Workspace* ws) {
   ws->entry_bag = static_cast<int32_t*>(take(n * 4));
   ws->entry_g2 = static_cast<float*>(take(n * 4));
   ws->hist_cap = static_cast<int64_t>(n / 16 + 4096);
-  ws->queue_cap = static_cast<int64_t>(n / kBucketSortCapacity + 2);
+  ws->queue_cap = static_cast<int64_t>(n / kBucketSortMaxGroup + 2);
   ws->hist = static_cast<int32_t*>(take(ws->hist_cap * 4));
   ws->bucket_start = static_cast<int32_t*>(take(ws->hist_cap * 4));
   ws->oversize = static_cast<int2*>(take(ws->queue_cap * sizeof(int2)));
@@ -160,7 +160,7 @@ int select_run_starts(Workspace& ws, int64_t N, cudaStream_t stream) {
 
 namespace {
 
-enum Opt { kSGD = 0, kExactAdagrad = 1 };
+enum Opt { kSGD = 0, kExactAdagrad = 1, kApproxAdagrad = 2 };
 
 constexpr int kDefaultLongSegment = 64;
 constexpr int kBwdThreads = 256;
@@ -236,7 +236,11 @@ struct BwdArgs {
   int32_t long_threshold;
   float lr, eps;
   uint64_t sr_seed, sr_offset;
+  const float* bag_g2;       // approximate Adagrad: squared gradient norm of every bag
 };
+
+// Step size of approximate rowwise Adagrad after the state has reached s.
+__device__ __forceinline__ float approx_step(const BwdArgs& a, float s) { return a.lr * (1.0f / (sqrtf(s) + a.eps)); }
 
 template <typename T, int VB, bool SR>
 __device__ __forceinline__ Raw<VB> pack_out(const typename Acc<T>::type* v, Philox* rng) {
@@ -373,10 +377,19 @@ __device__ __forceinline__ Tile load_tile(const uint32_t* __restrict__ keys, con
 // a 256-byte row needs only 4 lanes and a warp works on 8 runs at a time; each group keeps SEGS
 // runs in flight: the weight row, the optimizer state and the first two gradient rows of each are
 // requested first, then the runs are finished one after the other.
+//
+// Approximate rowwise Adagrad (OPT == kApproxAdagrad) applies every lookup of a row on its own:
+// state += g2(bag), row -= lr / (sqrt(state) + eps) * grad(bag), in bag order.  The state after the
+// k-th lookup of a run is state_0 plus a prefix sum of the bags' g2, so the whole run is again a
+// weighted sum of gradient rows: the tile computes the prefix sums with a segmented scan across its
+// lanes, turns them into per-entry step sizes, and the run reduction below uses them exactly as mean
+// pooling uses 1/L.
 template <typename T, int VB, int OPT, bool MEAN, bool SR, int SEGS, int VPL>
 __global__ void __launch_bounds__(kBwdThreads, 4) run_kernel(const BwdArgs a) {
   using acc_t = typename Acc<T>::type;
   constexpr int NE = VB / sizeof(T);
+  constexpr bool APPROX = OPT == kApproxAdagrad;
+  constexpr bool SCALED = MEAN || APPROX;  // every gradient row is multiplied by a per-entry factor
   const int lane = threadIdx.x & 31;
   const int lpr_log2 = a.lpr_log2;
   const int lpr = 1 << lpr_log2;
@@ -447,6 +460,20 @@ __global__ void __launch_bounds__(kBwdThreads, 4) run_kernel(const BwdArgs a) {
     const uint32_t my_row = key_to_row(a.table_offsets, a.idx_bits, valid ? cur.key : key0);
     acc_t my_scale = 1;
     const uint32_t my_goff = grad_units(static_cast<uint32_t>(valid ? cur.val : val0), &my_scale);
+    float my_state = 0.f;  // approximate Adagrad: the row's state after this entry's lookup
+    if (APPROX) {
+      float x = valid ? __ldg(a.bag_g2 + cur.val) : 0.f;
+      // inclusive scan inside runs: add the value `o` lanes back while that lane belongs to the same run
+      const unsigned upto = smask & ((lane >= 31) ? kFullMask : ((2u << lane) - 1u));
+      const int dist = upto ? lane - (31 - __clz(upto)) : 32;  // lanes since the run's start (32: it started in an earlier tile)
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float y = __shfl_up_sync(kFullMask, x, o);
+        if (dist < 32 && o <= dist) x += y;
+      }
+      my_state = a.state[my_row] + x;
+      my_scale = static_cast<acc_t>(approx_step(a, my_state));
+    }
     unsigned mine = smask & own_lanes;
     const int rounds = __reduce_max_sync(kFullMask, __popc(mine));
 
@@ -458,6 +485,7 @@ __global__ void __launch_bounds__(kBwdThreads, 4) run_kernel(const BwdArgs a) {
       Raw<VB> wraw[SEGS][VPL], g0[SEGS][VPL], g1[SEGS][VPL];
       acc_t s0[SEGS], s1[SEGS];
       float st_old[SEGS];
+      float st_run[SEGS];  // approximate Adagrad: state after the run's last lookup seen so far
 
       // phase 1: pick the runs and request their rows (an idle group re-reads lane 0's rows)
 #pragma unroll
@@ -472,10 +500,11 @@ __global__ void __launch_bounds__(kBwdThreads, 4) run_kernel(const BwdArgs a) {
         const uint32_t off0 = __shfl_sync(kFullMask, my_goff, i);
         const uint32_t off1 = __shfl_sync(kFullMask, my_goff, (i + 1) & 31);
         s0[q] = s1[q] = 1;
-        if (MEAN) {
+        if (SCALED) {
           s0[q] = __shfl_sync(kFullMask, my_scale, i);
           s1[q] = __shfl_sync(kFullMask, my_scale, (i + 1) & 31);
         }
+        if (APPROX) st_run[q] = __shfl_sync(kFullMask, my_state, (i + len[q] - 1) & 31);
         tail_lo[q] = tail_hi[q] = 0;
         if (has[q] && ((cmask >> i) & 1u)) {  // the run continues behind the tile (rare)
           tail_lo[q] = p0 + 32;
@@ -505,7 +534,7 @@ __global__ void __launch_bounds__(kBwdThreads, 4) run_kernel(const BwdArgs a) {
 #pragma unroll
         for (int j = 0; j < VPL; ++j) {
           unpack<T, VB>(g0[q][j], acc[j]);
-          if (MEAN) {
+          if (SCALED) {
 #pragma unroll
             for (int kk = 0; kk < NE; ++kk) acc[j][kk] *= s0[q];
           }
@@ -513,12 +542,12 @@ __global__ void __launch_bounds__(kBwdThreads, 4) run_kernel(const BwdArgs a) {
         const int maxlen = __reduce_max_sync(kFullMask, len[q]);
         if (maxlen > 1) {
 #pragma unroll
-          for (int j = 0; j < VPL; ++j) add_grad<T, VB, MEAN>(g1[q][j], s1[q], acc[j]);
+          for (int j = 0; j < VPL; ++j) add_grad<T, VB, SCALED>(g1[q][j], s1[q], acc[j]);
           for (int e = 2; e < maxlen; e += 2) {  // warp-uniform; runs of 3+ entries inside the tile
             const uint32_t o0 = __shfl_sync(kFullMask, my_goff, (first[q] + e) & 31);
             const uint32_t o1 = __shfl_sync(kFullMask, my_goff, (first[q] + e + 1) & 31);
             acc_t t0 = 1, t1 = 1;
-            if (MEAN) {
+            if (SCALED) {
               t0 = __shfl_sync(kFullMask, my_scale, (first[q] + e) & 31);
               t1 = __shfl_sync(kFullMask, my_scale, (first[q] + e + 1) & 31);
             }
@@ -532,16 +561,26 @@ __global__ void __launch_bounds__(kBwdThreads, 4) run_kernel(const BwdArgs a) {
             }
 #pragma unroll
             for (int j = 0; j < VPL; ++j) {
-              add_grad<T, VB, MEAN>(r0[j], t0, acc[j]);
-              add_grad<T, VB, MEAN>(r1[j], t1, acc[j]);
+              add_grad<T, VB, SCALED>(r0[j], t0, acc[j]);
+              add_grad<T, VB, SCALED>(r1[j], t1, acc[j]);
             }
           }
         }
         for (int p = tail_lo[q]; p < tail_hi[q]; p += 2) {  // group-uniform; entries behind the tile
           acc_t t0 = 1, t1 = 1;
           const bool two = p + 1 < tail_hi[q];
-          const uint32_t o0 = grad_units(static_cast<uint32_t>(__ldg(vals + p)), &t0);
-          const uint32_t o1 = two ? grad_units(static_cast<uint32_t>(__ldg(vals + p + 1)), &t1) : o0;
+          const uint32_t bag0 = static_cast<uint32_t>(__ldg(vals + p));
+          const uint32_t bag1 = two ? static_cast<uint32_t>(__ldg(vals + p + 1)) : bag0;
+          const uint32_t o0 = grad_units(bag0, &t0);
+          const uint32_t o1 = two ? grad_units(bag1, &t1) : o0;
+          if (APPROX) {  // the state keeps running through the entries behind the tile
+            st_run[q] += __ldg(a.bag_g2 + bag0);
+            t0 = static_cast<acc_t>(approx_step(a, st_run[q]));
+            if (two) {
+              st_run[q] += __ldg(a.bag_g2 + bag1);
+              t1 = static_cast<acc_t>(approx_step(a, st_run[q]));
+            }
+          }
           Raw<VB> r0[VPL], r1[VPL];
 #pragma unroll
           for (int j = 0; j < VPL; ++j) {
@@ -551,11 +590,15 @@ __global__ void __launch_bounds__(kBwdThreads, 4) run_kernel(const BwdArgs a) {
           }
 #pragma unroll
           for (int j = 0; j < VPL; ++j) {
-            add_grad<T, VB, MEAN>(r0[j], t0, acc[j]);
-            add_grad<T, VB, MEAN>(r1[j], t1, acc[j]);
+            add_grad<T, VB, SCALED>(r0[j], t0, acc[j]);
+            add_grad<T, VB, SCALED>(r1[j], t1, acc[j]);
           }
         }
         acc_t mult = static_cast<acc_t>(a.lr);
+        if (APPROX) {  // the step sizes are already inside the sum
+          mult = 1;
+          if (has[q] && sub == 0) a.state[wid[q]] = st_run[q];
+        }
         if (OPT == kExactAdagrad) {
           acc_t part = 0;
 #pragma unroll
@@ -728,6 +771,10 @@ template <typename T, int VB, int OPT, bool MEAN, bool SR>
 __global__ void __launch_bounds__(kBwdThreads) long_run_kernel(const BwdArgs a) {
   using acc_t = typename Acc<T>::type;
   constexpr int NE = VB / sizeof(T);
+  constexpr bool APPROX = OPT == kApproxAdagrad;
+  constexpr bool SCALED = MEAN || APPROX;
+  __shared__ float scan_tot[kBwdThreads / 32];  // approximate Adagrad: block scan of the bags' g2
+  __shared__ float carry;                       // ... and the state reached at the end of the previous block of entries
   __shared__ acc_t part[kBwdThreads * NE];
   __shared__ int64_t entry_off[kBwdThreads];   // byte offset of the gradient row of an entry
   __shared__ acc_t entry_scale[kBwdThreads];   // 1/L of its bag (mean pooling)
@@ -747,6 +794,7 @@ __global__ void __launch_bounds__(kBwdThreads) long_run_kernel(const BwdArgs a) 
     const int s = run.x, len = run.y - run.x;
     const uint32_t row = key_to_row(a.table_offsets, a.idx_bits, __ldg(a.keys + s));
     char* wrow = static_cast<char*>(a.weights) + static_cast<int64_t>(row) * row_bytes;
+    const float st_first = APPROX ? a.state[row] : 0.f;  // read by every thread before thread 0 overwrites it
 
     // Folds the groups' partial sums for chunk c in group order; every thread of warp 0 ends with the
     // total of its own `sub`.  The run is taken 256 entries at a time: every thread first turns one
@@ -759,11 +807,14 @@ __global__ void __launch_bounds__(kBwdThreads) long_run_kernel(const BwdArgs a) 
       acc_t acc[NE];
 #pragma unroll
       for (int k = 0; k < NE; ++k) acc[k] = 0;
+      if (APPROX && threadIdx.x == 0) carry = st_first;
       for (int base = 0; base < len; base += kBwdThreads) {
         const int m = min(kBwdThreads, len - base);
         __syncthreads();  // the previous block of entries has been consumed
+        float g2 = 0.f;
         if (static_cast<int>(threadIdx.x) < m) {
           const uint32_t bag = static_cast<uint32_t>(__ldg(a.vals + s + base + threadIdx.x));
+          if (APPROX) g2 = __ldg(a.bag_g2 + bag);
           const uint32_t t = fastdiv(bag, a.divB);
           const uint32_t b = bag - t * static_cast<uint32_t>(a.B);
           entry_off[threadIdx.x] = (static_cast<int64_t>(b) * a.stride_b + static_cast<int64_t>(t) * a.stride_t) *
@@ -771,6 +822,24 @@ __global__ void __launch_bounds__(kBwdThreads) long_run_kernel(const BwdArgs a) 
           if (MEAN)
             entry_scale[threadIdx.x] =
                 acc_t(1) / static_cast<acc_t>(__ldg(a.offsets + bag + 1) - __ldg(a.offsets + bag));
+        }
+        if (APPROX) {
+          // state after every entry = state so far + inclusive prefix sum of g2 over the block, in a
+          // fixed order: shuffles inside a warp, then the totals of the warps in front
+          float incl = g2;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const float up = __shfl_up_sync(kFullMask, incl, o);
+            if (lane >= o) incl += up;
+          }
+          if (lane == 31) scan_tot[threadIdx.x >> 5] = incl;
+          __syncthreads();
+          float before = carry;
+          for (int w2 = 0; w2 < static_cast<int>(threadIdx.x >> 5); ++w2) before += scan_tot[w2];
+          const float st = before + incl;
+          entry_scale[threadIdx.x] = static_cast<acc_t>(approx_step(a, st));
+          __syncthreads();  // everyone has read `carry`
+          if (threadIdx.x == blockDim.x - 1) carry = st;
         }
         __syncthreads();
         for (int i = gid; i < m; i += groups * 8) {
@@ -784,11 +853,11 @@ __global__ void __launch_bounds__(kBwdThreads) long_run_kernel(const BwdArgs a) 
             if (iu < m && vact) {
               r[u] = ld_stream_hint<VB>(static_cast<const char*>(a.grad) + entry_off[iu] + static_cast<int64_t>(v) * VB,
                                         keep);
-              if (MEAN) sc[u] = entry_scale[iu];
+              if (SCALED) sc[u] = entry_scale[iu];
             }
           }
 #pragma unroll
-          for (int u = 0; u < 8; ++u) add_grad<T, VB, MEAN>(r[u], sc[u], acc);
+          for (int u = 0; u < 8; ++u) add_grad<T, VB, SCALED>(r[u], sc[u], acc);
         }
       }
       __syncthreads();  // previous use of `part` finished
@@ -821,6 +890,10 @@ __global__ void __launch_bounds__(kBwdThreads) long_run_kernel(const BwdArgs a) 
       const bool vact = v < a.nvec;
       acc_t tot[NE];
       reduce_chunk(c, tot);
+      if (APPROX) {  // the step sizes are inside the sum; `carry` holds the state after the whole run
+        mult = 1;
+        if (c == 0 && threadIdx.x == 0) a.state[row] = carry;
+      }
       if (threadIdx.x < 32) {
         if (OPT == kExactAdagrad && c == 0) {
           if (a.nchunks == 1) g2 = group_sum(vact ? sq_sum(tot, NE) : acc_t(0), lpr_log2);
@@ -864,6 +937,7 @@ int launch_runs(const BwdArgs& a, cudaStream_t stream) {
   if ((knob == 1 || knob == 2 || knob == 4) && knob <= vpl_max) vpl = knob;
   const int lanes_needed = (a.nvec + vpl - 1) / vpl;
   if (lanes_needed > 32) {
+    if (OPT == kApproxAdagrad) return fail(TBE_ERR_UNSUPPORTED, "rows this wide take the per-run approximate Adagrad path");
     kernel = run_kernel_wide<T, VB, OPT, MEAN, SR>;
   } else {
     int l = 0;
@@ -904,6 +978,11 @@ int launch_runs(const BwdArgs& a, cudaStream_t stream) {
 
 template <typename T, int VB, int OPT>
 int dispatch_flags(const BwdArgs& a, bool mean, bool sr, cudaStream_t stream) {
+  if constexpr (OPT == kApproxAdagrad) {  // sum pooling only
+    if (mean) return fail(TBE_ERR_UNSUPPORTED, "approximate rowwise Adagrad supports sum pooling only");
+    if (sr) return launch_runs<T, VB, OPT, false, true>(a, stream);
+    return launch_runs<T, VB, OPT, false, false>(a, stream);
+  }
   if (mean) {
     if (sr) return launch_runs<T, VB, OPT, true, true>(a, stream);
     return launch_runs<T, VB, OPT, true, false>(a, stream);
@@ -926,12 +1005,54 @@ int dispatch_bwd(const BwdArgs& a, int dtype, int vb, bool mean, bool sr, cudaSt
   return fail(TBE_ERR_INVALID_ARGUMENT, "unknown dtype %d", dtype);
 }
 
+// g2[bag] = squared norm of the bag's gradient row (approximate Adagrad).  A warp per bag.
+template <typename T, int VB>
+__global__ void __launch_bounds__(256) bag_g2_kernel(const BwdArgs a, int64_t nbags, float* __restrict__ g2) {
+  using acc_t = typename Acc<T>::type;
+  constexpr int NE = VB / sizeof(T);
+  const int lane = threadIdx.x & 31;
+  const int64_t wstride = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  for (int64_t bag = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); bag < nbags;
+       bag += wstride) {
+    const int64_t t = bag / a.B, b = bag - t * a.B;
+    const char* g = static_cast<const char*>(a.grad) + (b * a.stride_b + t * a.stride_t) * static_cast<int64_t>(sizeof(T));
+    acc_t part = 0;
+    for (int v = lane; v < a.nvec; v += 32) {
+      acc_t e[NE];
+      unpack<T, VB>(ld_stream<VB>(g + static_cast<int64_t>(v) * VB), e);
+#pragma unroll
+      for (int k = 0; k < NE; ++k) part += e[k] * e[k];
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) part += __shfl_xor_sync(kFullMask, part, m);
+    if (lane == 0) g2[bag] = static_cast<float>(part);
+  }
+}
+
+int launch_bag_g2(const BwdArgs& a, int dtype, int vb, int64_t nbags, float* g2, cudaStream_t stream) {
+  int64_t blocks = (nbags + 7) / 8;
+  const int64_t cap = static_cast<int64_t>(device_sm_count()) * 8;
+  if (blocks > cap) blocks = cap;
+  const unsigned grid = static_cast<unsigned>(blocks);
+  {
+    KernelTimer timer("bag_g2_kernel", stream);
+    if (dtype == TBE_F16 && vb == 16) bag_g2_kernel<__half, 16><<<grid, 256, 0, stream>>>(a, nbags, g2);
+    else if (dtype == TBE_F16) bag_g2_kernel<__half, 8><<<grid, 256, 0, stream>>>(a, nbags, g2);
+    else if (dtype == TBE_F32) bag_g2_kernel<float, 16><<<grid, 256, 0, stream>>>(a, nbags, g2);
+    else bag_g2_kernel<double, 16><<<grid, 256, 0, stream>>>(a, nbags, g2);
+  }
+  TBE_CHECK_LAUNCH("bag_g2_kernel");
+  return TBE_OK;
+}
+
 int exact_backward(int opt, const void* grad, int64_t stride_b, int64_t stride_t, void* weights,
                    const int32_t* table_offsets, const int32_t* indices, const int32_t* offsets, float* state,
                    int64_t T, int64_t B, int64_t D, int64_t N, int64_t total_rows, int dtype, int pooling,
                    float lr, float eps, int sr, uint64_t sr_seed, uint64_t sr_offset, int64_t max_rows_per_table,
                    int plan_ready, void* workspace, int64_t workspace_bytes, void* stream_v) {
-  const char* who = opt == kSGD ? "tbe_backward_sgd" : "tbe_backward_exact_rowwise_adagrad";
+  const char* who = opt == kSGD ? "tbe_backward_sgd"
+                    : opt == kExactAdagrad ? "tbe_backward_exact_rowwise_adagrad"
+                                           : "tbe_backward_approx_rowwise_adagrad";
   TBE_REQUIRE(grad && weights && table_offsets && offsets && (indices || N == 0), "%s: null pointer argument", who);
   int rc = check_sizes(who, T, B, N, total_rows);
   if (rc != TBE_OK) return rc;
@@ -991,10 +1112,36 @@ int exact_backward(int opt, const void* grad, int64_t stride_b, int64_t stride_t
   const bool mean = pooling == TBE_POOL_MEAN;
   const bool use_sr = sr != 0 && dtype == TBE_F16;
   if (opt == kSGD) return dispatch_bwd<kSGD>(a, dtype, g.vb, mean, use_sr, stream);
-  return dispatch_bwd<kExactAdagrad>(a, dtype, g.vb, mean, use_sr, stream);
+  if (opt == kExactAdagrad) return dispatch_bwd<kExactAdagrad>(a, dtype, g.vb, mean, use_sr, stream);
+  // approximate Adagrad: the bags' squared gradient norms go where the run-start list and the
+  // per-position arrays of the per-run path would be (3 N words, unused on this path)
+  const int64_t nbags = T * B;
+  if (nbags > 3 * N) return fail(TBE_ERR_UNSUPPORTED, "%s: more than three bags per lookup", who);
+  float* bag_g2 = reinterpret_cast<float*>(ws.seg_starts);
+  a.bag_g2 = bag_g2;
+  rc = launch_bag_g2(a, dtype, g.vb, nbags, bag_g2, stream);
+  if (rc != TBE_OK) return rc;
+  return dispatch_bwd<kApproxAdagrad>(a, dtype, g.vb, mean, use_sr, stream);
 }
 
 }  // namespace
+
+int approx_backward_sorted(const void* grad, int64_t stride_b, int64_t stride_t, void* weights,
+                           const int32_t* table_offsets, const int32_t* indices, const int32_t* offsets, float* state,
+                           int64_t T, int64_t B, int64_t D, int64_t N, int64_t total_rows, int dtype, float lr,
+                           float eps, int sr, uint64_t sr_seed, uint64_t sr_offset, int64_t max_rows_per_table,
+                           void* workspace, int64_t workspace_bytes, void* stream) {
+  // rows too wide for the lane-group kernel (more than 32 lanes of up to two vectors) keep the per-run path
+  const int64_t row_bytes = D * elem_size(dtype);
+  const int64_t nvec = row_bytes % 16 == 0 ? row_bytes / 16 : row_bytes / 8;
+  const int64_t vpl = (row_bytes % 16 == 0 && nvec % 2 == 0) ? 2 : 1;
+  if ((nvec + vpl - 1) / vpl > 32)
+    return fail(TBE_ERR_UNSUPPORTED, "rows this wide take the per-run approximate Adagrad path");
+  return exact_backward(kApproxAdagrad, grad, stride_b, stride_t, weights, table_offsets, indices, offsets, state, T, B,
+                        D, N, total_rows, dtype, TBE_POOL_SUM, lr, eps, sr, sr_seed, sr_offset, max_rows_per_table,
+                        /*plan_ready=*/0, workspace, workspace_bytes, stream);
+}
+
 }  // namespace tbe
 
 extern "C" int64_t tbe_backward_workspace_bytes(int64_t N, int64_t total_rows) {

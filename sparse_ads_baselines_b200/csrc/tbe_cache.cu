@@ -194,23 +194,52 @@ __global__ void __launch_bounds__(256) cache_update_kernel(const CacheArgs a) {
   }
 }
 
+// A lane group of 2^lpr_log2 lanes (one 16-byte vector each) owns a claim; a warp therefore works on
+// 32 >> lpr_log2 claims at once and every group keeps kFillBatch claims in flight: all victim rows
+// (HBM) and all new rows (host link) of a batch are requested before the first store, so the host
+// link sees kFillBatch * 32 lanes of outstanding reads per warp instead of one row.  Claims never
+// alias: a row fetched in this step was not cached, a row evicted in this step was not looked up.
+constexpr int kFillBatch = 4;
+
 template <int VB>
-__global__ void __launch_bounds__(256) cache_fill_kernel(const CacheArgs a, int64_t row_bytes) {
-  const int lane = threadIdx.x & 31;
+__global__ void __launch_bounds__(256) cache_fill_kernel(const CacheArgs a, int64_t row_bytes, int lpr_log2) {
+  const int lpr = 1 << lpr_log2;
+  const int sub = threadIdx.x & (lpr - 1);
+  const int64_t group = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> lpr_log2;
+  const int64_t ngroups = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> lpr_log2;
   const int nclaims = a.counters[2];
-  const int64_t wstride = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
-  for (int64_t c = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); c < nclaims;
-       c += wstride) {
-    const int4 cl = a.claims[c];
-    char* crow = static_cast<char*>(a.cache_rows) + static_cast<int64_t>(cl.x) * row_bytes;
-    if (cl.y >= 0 && a.dirty[cl.x]) {
-      char* hrow = static_cast<char*>(a.host_rows) + static_cast<int64_t>(cl.y) * row_bytes;
-      for (int v = lane; v < a.nvec; v += 32) st_row<VB>(hrow + v * VB, ld_rw<VB>(crow + v * VB));
+  for (int64_t c0 = group; c0 < nclaims; c0 += ngroups * kFillBatch) {
+    int4 cl[kFillBatch];
+    bool live[kFillBatch], back[kFillBatch];
+#pragma unroll
+    for (int u = 0; u < kFillBatch; ++u) {
+      const int64_t c = c0 + u * ngroups;
+      live[u] = c < nclaims;
+      cl[u] = live[u] ? a.claims[c] : make_int4(0, -1, 0, 0);
+      back[u] = live[u] && cl[u].y >= 0 && a.dirty[cl[u].x] != 0;
     }
-    __syncwarp();
-    const char* nrow = static_cast<const char*>(a.host_rows) + static_cast<int64_t>(cl.z) * row_bytes;
-    for (int v = lane; v < a.nvec; v += 32) st_row<VB>(crow + v * VB, ld_rw<VB>(nrow + v * VB));
-    if (lane == 0) a.dirty[cl.x] = 0;
+    for (int v = sub; v < a.nvec; v += lpr) {
+      Raw<VB> old_row[kFillBatch], new_row[kFillBatch];
+#pragma unroll
+      for (int u = 0; u < kFillBatch; ++u) {
+        char* crow = static_cast<char*>(a.cache_rows) + static_cast<int64_t>(cl[u].x) * row_bytes;
+        const char* nrow = static_cast<const char*>(a.host_rows) + static_cast<int64_t>(cl[u].z) * row_bytes;
+        old_row[u] = raw_zero<VB>();
+        new_row[u] = raw_zero<VB>();
+        if (back[u]) old_row[u] = ld_rw<VB>(crow + static_cast<int64_t>(v) * VB);
+        if (live[u]) new_row[u] = ld_stream<VB>(nrow + static_cast<int64_t>(v) * VB);
+      }
+#pragma unroll
+      for (int u = 0; u < kFillBatch; ++u) {
+        char* crow = static_cast<char*>(a.cache_rows) + static_cast<int64_t>(cl[u].x) * row_bytes;
+        char* hrow = static_cast<char*>(a.host_rows) + static_cast<int64_t>(cl[u].y) * row_bytes;
+        if (back[u]) st_row<VB>(hrow + static_cast<int64_t>(v) * VB, old_row[u]);
+        if (live[u]) st_row<VB>(crow + static_cast<int64_t>(v) * VB, new_row[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kFillBatch; ++u)
+      if (live[u] && sub == 0) a.dirty[cl[u].x] = 0;
   }
 }
 
@@ -241,11 +270,19 @@ struct CachedRowArgs {
   int32_t B, T, D, nvec, mean;
 };
 
+// One warp per bag.  Every lane first resolves one lookup of the bag to the address of its row (the
+// cache slot, or the host table when the row is uncached); a row is then fetched by a group of
+// 2^lpr_log2 lanes, so a warp gathers 32 >> lpr_log2 rows per step and keeps four steps in flight.
 template <typename T, int VB>
-__global__ void __launch_bounds__(256) cached_forward_kernel(const CachedRowArgs a) {
+__global__ void __launch_bounds__(256) cached_forward_kernel(const CachedRowArgs a, int lpr_log2) {
   using acc_t = typename Acc<T>::type;
   constexpr int NE = VB / sizeof(T);
+  constexpr int kInFlight = 4;
   const int lane = threadIdx.x & 31;
+  const int lpr = 1 << lpr_log2;
+  const int sub = lane & (lpr - 1);
+  const int slot = lane >> lpr_log2;
+  const int rps = 32 >> lpr_log2;  // rows per warp step
   const int64_t nbags = static_cast<int64_t>(a.B) * a.T;
   const int64_t wstride = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
   const int64_t row_bytes = static_cast<int64_t>(a.D) * sizeof(T);
@@ -256,29 +293,46 @@ __global__ void __launch_bounds__(256) cached_forward_kernel(const CachedRowArgs
     const uint32_t row0 = static_cast<uint32_t>(__ldg(a.table_offsets + t));
     const int s = __ldg(a.offsets + bag), e = __ldg(a.offsets + bag + 1);
     char* out = static_cast<char*>(a.out) + (static_cast<int64_t>(b) * a.T + t) * row_bytes;
-    for (int v = lane; v < a.nvec || v == lane; v += 32) {
+    for (int c = 0; c * 32 < a.nvec; ++c) {  // rows wider than 32 vectors are walked in chunks (lpr = 32 then)
+      const int v = c * 32 + sub;
       const bool vact = v < a.nvec;
       acc_t acc[NE];
 #pragma unroll
       for (int k = 0; k < NE; ++k) acc[k] = 0;
-      for (int p = s; p < e; ++p) {
-        const int where = __ldg(a.loc + p);
-        const char* row = where >= 0
-                              ? static_cast<const char*>(a.cache_rows) + static_cast<int64_t>(where) * row_bytes
-                              : static_cast<const char*>(a.host_rows) +
-                                    static_cast<int64_t>(row0 + static_cast<uint32_t>(__ldg(a.indices + p))) * row_bytes;
-        if (vact) {
-          acc_t x[NE];
-          unpack<T, VB>(ld_rw<VB>(row + static_cast<int64_t>(v) * VB), x);
-#pragma unroll
-          for (int k = 0; k < NE; ++k) acc[k] += x[k];
+      for (int base = s; base < e; base += 32) {
+        const int p = base + lane;
+        uint64_t rowp = 0;
+        if (p < e) {
+          const int where = __ldg(a.loc + p);
+          rowp = where >= 0 ? reinterpret_cast<uint64_t>(a.cache_rows) + static_cast<uint64_t>(where) * row_bytes
+                            : reinterpret_cast<uint64_t>(a.host_rows) +
+                                  static_cast<uint64_t>(row0 + static_cast<uint32_t>(__ldg(a.indices + p))) * row_bytes;
         }
+        const int cnt = min(32, e - base);
+        for (int j0 = 0; j0 < cnt; j0 += rps * kInFlight) {
+          Raw<VB> r[kInFlight];
+#pragma unroll
+          for (int u = 0; u < kInFlight; ++u) {
+            const int j = j0 + u * rps + slot;
+            const uint32_t lo = __shfl_sync(kFullMask, static_cast<uint32_t>(rowp), j & 31);
+            const uint32_t hi = __shfl_sync(kFullMask, static_cast<uint32_t>(rowp >> 32), j & 31);
+            const char* row = reinterpret_cast<const char*>((static_cast<uint64_t>(hi) << 32) | lo);
+            r[u] = raw_zero<VB>();
+            if (j < cnt && vact) r[u] = ld_rw<VB>(row + static_cast<int64_t>(v) * VB);
+          }
+#pragma unroll
+          for (int u = 0; u < kInFlight; ++u) accumulate<T, VB>(r[u], acc);
+        }
+      }
+      for (int m = lpr; m < 32; m <<= 1) {  // fold the row slots of the warp together
+#pragma unroll
+        for (int k = 0; k < NE; ++k) acc[k] += __shfl_xor_sync(kFullMask, acc[k], m);
       }
       if (a.mean && e > s) {
 #pragma unroll
         for (int k = 0; k < NE; ++k) acc[k] = acc[k] / static_cast<acc_t>(e - s);
       }
-      if (vact) st_row<VB>(out + static_cast<int64_t>(v) * VB, pack_rn<T, VB>(acc));
+      if (slot == 0 && vact) st_row<VB>(out + static_cast<int64_t>(v) * VB, pack_rn<T, VB>(acc));
     }
   }
 }
@@ -553,7 +607,7 @@ extern "C" int tbe_cache_prefetch(void* cache_rows, int32_t* tags, int32_t* last
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   TBE_CUDA_TRY(cudaMemsetAsync(cs.ws.counters, 0, 64, stream));
   if (N == 0) {
-    TBE_CUDA_TRY(cudaMemsetAsync(stats, 0, 16, stream));
+    TBE_CUDA_TRY(cudaMemsetAsync(stats, 0, 5 * sizeof(int32_t), stream));
     return TBE_OK;
   }
   int vb = 16, nvec = 0;
@@ -615,12 +669,14 @@ extern "C" int tbe_cache_prefetch(void* cache_rows, int32_t* tags, int32_t* last
   }
   TBE_CHECK_LAUNCH("cache_update_kernel");
   const int64_t row_bytes = D * elem_size(dtype);
+  int fill_lpr_log2 = 0;
+  while ((1 << fill_lpr_log2) < nvec && fill_lpr_log2 < 5) ++fill_lpr_log2;
   {
     KernelTimer timer("cache_fill_kernel", stream);
     if (vb == 16) {
-      cache_fill_kernel<16><<<grid_for(N), 256, 0, stream>>>(a, row_bytes);
+      cache_fill_kernel<16><<<grid_for(N), 256, 0, stream>>>(a, row_bytes, fill_lpr_log2);
     } else {
-      cache_fill_kernel<8><<<grid_for(N), 256, 0, stream>>>(a, row_bytes);
+      cache_fill_kernel<8><<<grid_for(N), 256, 0, stream>>>(a, row_bytes, fill_lpr_log2);
     }
   }
   TBE_CHECK_LAUNCH("cache_fill_kernel");
@@ -665,9 +721,11 @@ extern "C" int tbe_cache_forward(const void* cache_rows, const void* host_rows, 
   {
     KernelTimer timer("cached_forward_kernel", stream);
     const int grid = grid_for(T * B);
-    if (dtype == TBE_F16 && vb == 16) cached_forward_kernel<__half, 16><<<grid, 256, 0, stream>>>(a);
-    else if (dtype == TBE_F16) cached_forward_kernel<__half, 8><<<grid, 256, 0, stream>>>(a);
-    else if (dtype == TBE_F32) cached_forward_kernel<float, 16><<<grid, 256, 0, stream>>>(a);
+    int lpr_log2 = 0;
+    while ((1 << lpr_log2) < nvec && lpr_log2 < 5) ++lpr_log2;
+    if (dtype == TBE_F16 && vb == 16) cached_forward_kernel<__half, 16><<<grid, 256, 0, stream>>>(a, lpr_log2);
+    else if (dtype == TBE_F16) cached_forward_kernel<__half, 8><<<grid, 256, 0, stream>>>(a, lpr_log2);
+    else if (dtype == TBE_F32) cached_forward_kernel<float, 16><<<grid, 256, 0, stream>>>(a, lpr_log2);
     else return fail(TBE_ERR_UNSUPPORTED, "%s: fp16 and fp32 tables only", who);
   }
   TBE_CHECK_LAUNCH("cached_forward_kernel");

@@ -24,6 +24,10 @@ struct FwdArgs {
   int32_t B_local, T_total, t0;
   int32_t lpr_log2, nvec, nchunks;
   int64_t out_stride_b_bytes;  // distance between the output rows of consecutive samples (unsharded)
+  // tables of different width (MIXED): element offset of every table in the flat weights vector and
+  // first output column of every table, both [T + 1]
+  const int64_t* weight_offsets;
+  const int32_t* dim_offsets;
 };
 
 template <typename T>
@@ -35,7 +39,11 @@ __device__ __forceinline__ float to_acc<__half>(__half x) {
   return __half2float(x);
 }
 
-template <typename T, int VB, bool WEIGHTED, bool MEAN, bool SHARDED, int UNROLL>
+//
+// MIXED: every table has its own width.  The row geometry (lanes per row, vectors, chunks), the
+// table's base address and the output column are then derived per bag from dim_offsets /
+// weight_offsets instead of once per launch; everything else is the same walk.
+template <typename T, int VB, bool WEIGHTED, bool MEAN, bool SHARDED, int UNROLL, bool MIXED = false>
 __global__ void __launch_bounds__(256) tbe_forward_kernel(const FwdArgs a) {
   using acc_t = typename Acc<T>::type;
   constexpr int NE = VB / sizeof(T);
@@ -47,12 +55,13 @@ __global__ void __launch_bounds__(256) tbe_forward_kernel(const FwdArgs a) {
   int64_t bag = static_cast<int64_t>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
   if (bag >= nbags) return;
 
-  const int lpr_log2 = a.lpr_log2;
-  const int rps_log2 = 5 - lpr_log2;  // log2(rows per warp step)
-  const int sub = lane & ((1 << lpr_log2) - 1);
-  const int slot = lane >> lpr_log2;
+  int lpr_log2 = a.lpr_log2;
+  int rps_log2 = 5 - lpr_log2;  // log2(rows per warp step)
+  int sub = lane & ((1 << lpr_log2) - 1);
+  int slot = lane >> lpr_log2;
   const char* __restrict__ W = static_cast<const char*>(a.weights);
-  const uint32_t row_bytes = static_cast<uint32_t>(a.D) * static_cast<uint32_t>(sizeof(T));
+  uint32_t row_bytes = static_cast<uint32_t>(a.D) * static_cast<uint32_t>(sizeof(T));
+  int nvec = a.nvec, nchunks = a.nchunks;
   const int32_t* __restrict__ offsets = a.offsets;
   const int32_t* __restrict__ indices = a.indices;
   const T* __restrict__ psw = static_cast<const T*>(a.psw);
@@ -79,10 +88,24 @@ __global__ void __launch_bounds__(256) tbe_forward_kernel(const FwdArgs a) {
 
     const int t = static_cast<int>(bag / a.B);
     const int b = static_cast<int>(bag - static_cast<int64_t>(t) * a.B);
-    const uint32_t row0 = static_cast<uint32_t>(__ldg(a.table_offsets + t));
+    uint32_t row0 = 0;
+    if (!MIXED) row0 = static_cast<uint32_t>(__ldg(a.table_offsets + t));
 
     char* outp;
-    if (SHARDED) {
+    if (MIXED) {
+      const int32_t d0 = __ldg(a.dim_offsets + t);
+      row_bytes = static_cast<uint32_t>(__ldg(a.dim_offsets + t + 1) - d0) * static_cast<uint32_t>(sizeof(T));
+      nvec = static_cast<int>(row_bytes / VB);
+      nchunks = (nvec + 31) >> 5;
+      lpr_log2 = 0;
+      while ((1 << lpr_log2) < nvec && lpr_log2 < 5) ++lpr_log2;
+      rps_log2 = 5 - lpr_log2;
+      sub = lane & ((1 << lpr_log2) - 1);
+      slot = lane >> lpr_log2;
+      W = static_cast<const char*>(a.weights) + __ldg(a.weight_offsets + t) * static_cast<int64_t>(sizeof(T));
+      outp = static_cast<char*>(a.out[0]) + static_cast<int64_t>(b) * a.out_stride_b_bytes +
+             static_cast<int64_t>(d0) * static_cast<int64_t>(sizeof(T));
+    } else if (SHARDED) {
       const int dest = b / a.B_local;
       const int bl = b - dest * a.B_local;
       outp = static_cast<char*>(a.out[dest]) +
@@ -92,9 +115,9 @@ __global__ void __launch_bounds__(256) tbe_forward_kernel(const FwdArgs a) {
              static_cast<int64_t>(t) * static_cast<int64_t>(row_bytes);
     }
 
-    for (int c = 0; c < a.nchunks; ++c) {
+    for (int c = 0; c < nchunks; ++c) {
       const int v = (c << 5) + sub;
-      const bool vact = v < a.nvec;
+      const bool vact = v < nvec;
       // this lane's vector of row 0; lanes past the end of the row re-read vector 0 and never store
       const char* const Wv = W + (vact ? static_cast<int64_t>(v) * VB : 0);
       acc_t acc[NE];
@@ -332,4 +355,59 @@ extern "C" int tbe_forward_sharded(const void* weights, const int32_t* table_off
                                    int dtype, int pooling, void* stream) {
   return tbe::forward_common(weights, table_offsets, indices, offsets, per_sample_weights, peer_outputs,
                              world, T, B, D, T_total, t0, dtype, pooling, true, 0, stream);
+}
+
+extern "C" int tbe_forward_mixed(const void* weights, const int64_t* weight_offsets, const int32_t* dim_offsets,
+                                 const int32_t* indices, const int32_t* offsets, const void* per_sample_weights,
+                                 void* output, int64_t T, int64_t B, int64_t total_D, int dtype, int vector_bytes,
+                                 void* stream) {
+  using namespace tbe;
+  TBE_REQUIRE(weights && weight_offsets && dim_offsets && offsets && output, "tbe_forward_mixed: null pointer argument");
+  TBE_REQUIRE(T > 0 && B > 0 && total_D > 0 && B * T < (1ll << 31), "tbe_forward_mixed: bad sizes");
+  TBE_REQUIRE(dtype == TBE_F32 || dtype == TBE_F16 || dtype == TBE_F64, "tbe_forward_mixed: bad dtype %d", dtype);
+  TBE_REQUIRE(vector_bytes == 16 || (vector_bytes == 8 && dtype == TBE_F16),
+              "tbe_forward_mixed: vector_bytes must be 16 (8 is allowed for fp16 rows that are only 8-byte aligned)");
+  TBE_REQUIRE(reinterpret_cast<uintptr_t>(weights) % vector_bytes == 0 &&
+                  reinterpret_cast<uintptr_t>(output) % vector_bytes == 0 &&
+                  (total_D * elem_size(dtype)) % vector_bytes == 0,
+              "tbe_forward_mixed: weights, output and output rows must be %d-byte aligned", vector_bytes);
+  FwdArgs a{};
+  a.weights = weights;
+  a.weight_offsets = weight_offsets;
+  a.dim_offsets = dim_offsets;
+  a.indices = indices;
+  a.offsets = offsets;
+  a.psw = per_sample_weights;
+  a.out[0] = output;
+  a.B = static_cast<int32_t>(B);
+  a.T = static_cast<int32_t>(T);
+  a.out_stride_b_bytes = total_D * elem_size(dtype);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool weighted = per_sample_weights != nullptr;
+  void (*kernel)(const FwdArgs) = nullptr;
+  if (dtype == TBE_F16 && vector_bytes == 16)
+    kernel = weighted ? tbe_forward_kernel<__half, 16, true, false, false, 4, true>
+                      : tbe_forward_kernel<__half, 16, false, false, false, 4, true>;
+  else if (dtype == TBE_F16)
+    kernel = weighted ? tbe_forward_kernel<__half, 8, true, false, false, 4, true>
+                      : tbe_forward_kernel<__half, 8, false, false, false, 4, true>;
+  else if (dtype == TBE_F32)
+    kernel = weighted ? tbe_forward_kernel<float, 16, true, false, false, 4, true>
+                      : tbe_forward_kernel<float, 16, false, false, false, 4, true>;
+  else
+    kernel = weighted ? tbe_forward_kernel<double, 16, true, false, false, 4, true>
+                      : tbe_forward_kernel<double, 16, false, false, false, 4, true>;
+  int per_sm = 0;
+  TBE_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, 0));
+  if (per_sm < 1) per_sm = 1;
+  const int64_t nbags = B * T;
+  int64_t blocks = (nbags + 7) / 8;
+  const int64_t resident = static_cast<int64_t>(device_sm_count()) * per_sm;
+  if (blocks > resident) blocks = resident;
+  {
+    KernelTimer timer("tbe_forward_kernel", s);
+    kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(a);
+  }
+  TBE_CHECK_LAUNCH("tbe_forward_kernel");
+  return TBE_OK;
 }

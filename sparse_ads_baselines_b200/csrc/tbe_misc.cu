@@ -16,6 +16,23 @@ __global__ void construct_offsets_kernel(const int32_t* __restrict__ begin,   //
   out[1 + i] = hi - __ldg(begin + i);
 }
 
+// Bag-wise gather of ragged index lists: destination bag g takes the indices of source bag
+// src_bag[g].  One warp per destination bag.
+__global__ void __launch_bounds__(256) permute_bags_kernel(const int32_t* __restrict__ src_indices,
+                                                          const int32_t* __restrict__ src_offsets,
+                                                          const int32_t* __restrict__ src_bag,
+                                                          const int32_t* __restrict__ dst_offsets,
+                                                          int32_t* __restrict__ dst_indices, int64_t nbags) {
+  const int lane = threadIdx.x & 31;
+  const int64_t wstride = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  for (int64_t g = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); g < nbags; g += wstride) {
+    const int32_t sb = __ldg(src_bag + g);
+    const int32_t s = __ldg(src_offsets + sb), n = __ldg(src_offsets + sb + 1) - s;
+    const int32_t d = __ldg(dst_offsets + g);
+    for (int32_t i = lane; i < n; i += 32) dst_indices[d + i] = __ldg(src_indices + s + i);
+  }
+}
+
 // err[0] = violation kind (first writer wins), err[1..3] = details.
 enum Violation { kNone = 0, kFirstOffset = 1, kDecreasing = 2, kLastOffset = 3, kIndexRange = 4 };
 
@@ -103,4 +120,23 @@ extern "C" int tbe_check_inputs(const int32_t* indices, const int32_t* offsets, 
     case kLastOffset: return fail(TBE_ERR_BAD_INPUT_DATA, "offsets[T*B] is %d, expected N = %d", a, b);
     default: return fail(TBE_ERR_BAD_INPUT_DATA, "indices[%d] = %d is outside table %d", a, b, c);
   }
+}
+
+extern "C" int tbe_permute_bags(const int32_t* src_indices, const int32_t* src_offsets, const int32_t* src_bag,
+                                const int32_t* dst_offsets, int32_t* dst_indices, int64_t nbags, void* stream_v) {
+  using namespace tbe;
+  TBE_REQUIRE(src_offsets && src_bag && dst_offsets, "tbe_permute_bags: null pointer argument");
+  TBE_REQUIRE(nbags >= 0 && nbags < (1ll << 31), "tbe_permute_bags: bag count out of range");
+  if (nbags == 0) return TBE_OK;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  int64_t blocks = (nbags + 7) / 8;
+  const int64_t cap = static_cast<int64_t>(device_sm_count()) * 8;
+  if (blocks > cap) blocks = cap;
+  {
+    KernelTimer timer("permute_bags_kernel", stream);
+    permute_bags_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(src_indices, src_offsets, src_bag,
+                                                                          dst_offsets, dst_indices, nbags);
+  }
+  TBE_CHECK_LAUNCH("permute_bags_kernel");
+  return TBE_OK;
 }

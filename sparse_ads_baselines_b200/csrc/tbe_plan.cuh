@@ -38,6 +38,9 @@ KeyLayout key_layout(int64_t T, int64_t total_rows, int64_t max_rows_per_table, 
 
 // Largest bucket the two-level sort finishes in shared memory.
 constexpr int kBucketSortCapacity = 2048;
+// Most pairs of a bucket that may share one of its level-2 counters (a hot row); a bucket beyond
+// either limit is queued for the oversize path, so the queue needs a slot per kBucketSortMaxGroup pairs.
+constexpr int kBucketSortMaxGroup = 256;
 
 // Two-level sort geometry: bucket = index >> shift, nb buckets and `slices` position ranges per table.
 struct BucketGeometry {
@@ -61,6 +64,15 @@ int prepare_workspace(const char* who, void* workspace, int64_t workspace_bytes,
 int sort_pairs(Workspace& ws, int64_t N, int sort_bits, cudaStream_t stream);
 // seg_starts[0..U) = first position of every run of equal sorted keys, counters[0] = U.
 int select_run_starts(Workspace& ws, int64_t N, cudaStream_t stream);
+
+// Approximate rowwise Adagrad without per-sample weights on the sorted-run kernels of tbe_backward.cu
+// (the bags' squared gradient norms, a prefix sum per run, then a weighted segmented reduction).
+// Returns TBE_ERR_UNSUPPORTED for shapes that path does not take; the caller then uses its own.
+int approx_backward_sorted(const void* grad, int64_t stride_b, int64_t stride_t, void* weights,
+                           const int32_t* table_offsets, const int32_t* indices, const int32_t* offsets, float* state,
+                           int64_t T, int64_t B, int64_t D, int64_t N, int64_t total_rows, int dtype, float lr,
+                           float eps, int sr, uint64_t sr_seed, uint64_t sr_offset, int64_t max_rows_per_table,
+                           void* workspace, int64_t workspace_bytes, void* stream);
 
 // Row of `weights` a sort key stands for.
 __device__ __forceinline__ uint32_t key_to_row(const int32_t* __restrict__ table_offsets, int idx_bits, uint32_t key) {

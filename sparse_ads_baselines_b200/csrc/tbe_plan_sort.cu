@@ -16,14 +16,14 @@
 //                              also replaces the separate linearize pass.  The order inside a
 //                              slice's share is whatever the shared-memory atomics gave; level 2
 //                              makes that irrelevant.
-//   3. bucket_rank_kernel    : one CTA per bucket.  A counting sort on the low `shift` index bits in
-//                              shared memory (one 16-bit counter per possible row of the bucket)
-//                              brings equal rows together; pairs that share a row are then ranked
+//   3. bucket_rank_kernel    : one CTA per bucket.  A counting sort in shared memory on coarse
+//                              counters (one per small group of neighbouring rows) brings the
+//                              pairs of a group together; groups with several pairs are then ranked
 //                              by (key, bag id).  Equal pairs are indistinguishable, so the output
 //                              is the unique order by (table, index, bag): exactly what a stable
 //                              sort of the position-ordered input gives, and independent of how the
 //                              atomics of any step were served.  A bucket larger than the CTA's
-//                              capacity is queued instead ...
+//                              capacity, or with a hot row, is queued instead ...
 //   4. oversize_sort_kernel  : ... and sorted by a 1024-thread CTA with stable 8-bit radix passes
 //                              through global memory, first on the bag id, then on the index bits.
 //                              Skewed batches, where a few hot rows put most of a table in one
@@ -43,7 +43,9 @@ constexpr int kScatterTileWide = 4096;  // ... when a table has more than kFewBu
 constexpr int kRankThreads = 256;
 constexpr int kRankItems = kBucketSortCapacity / kRankThreads;  // pairs a thread holds
 constexpr int kRankBits = 14;                                   // most index bits level 2 can count on
-constexpr int kRankWords = (1 << kRankBits) / 2;                // two 16-bit counters per word
+constexpr int kRankCounterBits = 13;                            // level 2 keeps at most 8192 counters per bucket
+constexpr int kRankMaxGroup = kBucketSortMaxGroup;              // most pairs one counter may collect
+static_assert(kBucketSortCapacity <= 2048 && kRankMaxGroup < 1024, "packing of bucket_rank_kernel's `where`");
 constexpr int kOversizeThreads = 1024;
 constexpr int kOversizeWarps = kOversizeThreads / 32;
 constexpr int kMaxDigits = 256;             // radix passes look at up to 8 bits
@@ -348,29 +350,41 @@ __global__ void __launch_bounds__(kScatterThreads, NBCAP <= kFewBuckets ? 3 : 2)
 __device__ __forceinline__ int swizzle_chunk(int c) { return c ^ ((c >> 3) & 7); }
 __device__ __forceinline__ int swizzle_word(int i) { return (swizzle_chunk(i >> 2) << 2) | (i & 3); }
 
-// Dynamic shared memory: a region that first holds `words` counter words (two 16-bit counters each)
-// and later the list of pairs that share their row with another pair, then the bucket's keys and
+// Level 2, one CTA per bucket of at most kBucketSortCapacity pairs.
+//
+// A counting sort with one counter per possible row would spend most of its time on counters, not on
+// pairs: a bucket of the usual sparse batch holds 1,300 pairs spread over 16,384 rows.  So the
+// counters are coarse: one per group of 2^cshift consecutive rows, at most kRankCounters per bucket
+// (about 0.6 pairs per counter).  The counting sort brings the pairs of a group together; groups that
+// hold several pairs (rows that repeat, or neighbouring rows) are then put in (key, bag id) order by
+// ranking every pair against its group, still in shared memory, and the bucket leaves with one
+// coalesced copy.  Equal pairs are indistinguishable, so the result is the unique order by
+// (table, index, bag id).  A group above kRankMaxGroup pairs (a hot row) would make the ranking
+// quadratic: such a bucket is queued for oversize_sort_kernel like one that exceeds the capacity.
+//
+// Dynamic shared memory: `words` counter words (two 16-bit counters each), then the bucket's keys and
 // values in counting-sort order.
 __global__ void __launch_bounds__(kRankThreads) bucket_rank_kernel(
     const int32_t* __restrict__ bucket_start, const uint2* __restrict__ pairs, uint32_t* __restrict__ kout,
-    int32_t* __restrict__ vout, int bits, int words, int region_words, int32_t* __restrict__ queue_count,
+    int32_t* __restrict__ vout, int bits, int cshift, int words, int32_t* __restrict__ queue_count,
     int2* __restrict__ queue, int queue_cap) {
   extern __shared__ uint4 smem4[];
   uint32_t* cnt = reinterpret_cast<uint32_t*>(smem4);
-  uint32_t* list = cnt;
-  uint32_t* sk = cnt + region_words;
+  uint32_t* sk = cnt + words;
   int32_t* sv = reinterpret_cast<int32_t*>(sk + kBucketSortCapacity);
   __shared__ uint32_t warp_tot[kRankThreads / 32];
-  __shared__ int list_n;
 
   const int32_t start = __ldg(bucket_start + blockIdx.x), end = __ldg(bucket_start + blockIdx.x + 1);
   const int32_t n = end - start;
   if (n <= 0) return;
-  if (n > kBucketSortCapacity) {
+  auto enqueue = [&]() {
     if (threadIdx.x == 0) {
       const int q = atomicAdd(queue_count, 1);
-      if (q < queue_cap) queue[q] = make_int2(start, end);  // always true: fewer than N / capacity such buckets
+      if (q < queue_cap) queue[q] = make_int2(start, end);  // always true: the queue has a slot per possible bucket
     }
+  };
+  if (n > kBucketSortCapacity) {
+    enqueue();
     return;
   }
   pairs += start;
@@ -386,25 +400,26 @@ __global__ void __launch_bounds__(kRankThreads) bucket_rank_kernel(
     val[j] = static_cast<int32_t>(pr.y);
   }
   const uint32_t low_mask = (1u << bits) - 1u;
+  const uint32_t last_counter = low_mask >> cshift;
   const int chunks = words >> 2;
   const int cpt = (chunks + kRankThreads - 1) / kRankThreads;  // chunks a thread zeroes and scans
   const int c0 = threadIdx.x * cpt;
   for (int c = c0; c < min(c0 + cpt, chunks); ++c) smem4[swizzle_chunk(c)] = make_uint4(0u, 0u, 0u, 0u);
-  if (threadIdx.x == 0) list_n = 0;
   __syncthreads();
 
-  // count: the old value of a pair's counter is its arrival number among the pairs of its row
+  // count: the old value of a pair's counter is its arrival number among the pairs of its group
 #pragma unroll
   for (int j = 0; j < kRankItems; ++j) {
     if (threadIdx.x + j * kRankThreads < n) {
-      const uint32_t low = key[j] & low_mask;
-      const int half = (low & 1u) * 16;
-      where[j] = (atomicAdd(&cnt[swizzle_word(low >> 1)], 1u << half) >> half) & 0xffffu;
+      const uint32_t c = (key[j] & low_mask) >> cshift;
+      const int half = (c & 1u) * 16;
+      where[j] = (atomicAdd(&cnt[swizzle_word(c >> 1)], 1u << half) >> half) & 0xffffu;
     }
   }
   __syncthreads();
 
-  // counts -> first position of every row, in place (positions fit 16 bits)
+  // counts -> first position of every group, in place (positions fit 16 bits)
+  bool big_group = false;
   {
     uint32_t packed = 0;
     for (int c = c0; c < min(c0 + cpt, chunks); ++c) {
@@ -418,6 +433,7 @@ __global__ void __launch_bounds__(kRankThreads) bucket_rank_kernel(
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const uint32_t lo = wv[i] & 0xffffu, hi = wv[i] >> 16;
+        big_group |= lo > kRankMaxGroup || hi > kRankMaxGroup;
         const uint32_t second = run + lo;
         wv[i] = run | (second << 16);
         run = second + hi;
@@ -425,65 +441,66 @@ __global__ void __launch_bounds__(kRankThreads) bucket_rank_kernel(
       smem4[swizzle_chunk(c)] = v;
     }
   }
-  __syncthreads();
+  if (__syncthreads_or(big_group)) {  // (also the barrier the placement below needs)
+    enqueue();
+    return;
+  }
 
-  // place in counting-sort order.  where = position | first position of the row << 16, top bit set
-  // when the row holds more than one pair (its next row starts more than one position later).
+  // place in counting-sort order.  where = position | first position of the group << 11 | pairs in
+  // the group << 22 (positions are below 2048, a group holds at most kRankMaxGroup pairs).
 #pragma unroll
   for (int j = 0; j < kRankItems; ++j) {
     if (threadIdx.x + j * kRankThreads < n) {
-      const uint32_t low = key[j] & low_mask;
-      const int word = low >> 1;
+      const uint32_t c = (key[j] & low_mask) >> cshift;
+      const int word = c >> 1;
       const uint32_t packed = cnt[swizzle_word(word)];
       uint32_t first, next;
-      if (low & 1u) {
+      if (c & 1u) {
         first = packed >> 16;
         next = word + 1 < words ? (cnt[swizzle_word(word + 1)] & 0xffffu) : static_cast<uint32_t>(n);
       } else {
         first = packed & 0xffffu;
         next = packed >> 16;
       }
-      if (low == low_mask) next = static_cast<uint32_t>(n);  // the last row of the bucket (bits may be 0)
+      if (c == last_counter) next = static_cast<uint32_t>(n);  // the last group of the bucket
       const uint32_t pos = first + where[j];
       sk[pos] = key[j];
       sv[pos] = val[j];
-      where[j] = pos | (first << 16) | (next - first > 1u ? 0x80000000u : 0u);
+      where[j] = pos | (first << 11) | ((next - first) << 22);
     }
   }
   __syncthreads();
 
-  // Copy out; rows with several pairs still need those ordered, so list their pairs (the counters are
-  // dead by now).
+  // groups of several pairs: every pair finds its rank by (key, bag id) among its group; among equal
+  // pairs the arrival order stands, which cannot be told apart in the output
 #pragma unroll
-  for (int j = 0; j < kRankItems; ++j)
-    if (threadIdx.x + j * kRankThreads < n && (where[j] & 0x80000000u))
-      list[atomicAdd(&list_n, 1)] = where[j] & 0x7fffffffu;
+  for (int j = 0; j < kRankItems; ++j) {
+    const uint32_t size = where[j] >> 22;
+    if (threadIdx.x + j * kRankThreads < n && size > 1u) {
+      const uint32_t pos = where[j] & 2047u, first = (where[j] >> 11) & 2047u;
+      const uint32_t k0 = key[j];
+      const int32_t v0 = val[j];
+      uint32_t rank = 0;
+      for (uint32_t q = first; q < first + size; ++q) {
+        const uint32_t kq = sk[q];
+        const int32_t vq = sv[q];
+        rank += (kq < k0) || (kq == k0 && (vq < v0 || (vq == v0 && q < pos)));
+      }
+      where[j] = (where[j] & ~2047u) | (first + rank);
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < kRankItems; ++j) {
+    if (threadIdx.x + j * kRankThreads < n && (where[j] >> 22) > 1u) {
+      sk[where[j] & 2047u] = key[j];
+      sv[where[j] & 2047u] = val[j];
+    }
+  }
+  __syncthreads();
   for (int i = threadIdx.x; i < n; i += kRankThreads) {
     kout[i] = sk[i];
     vout[i] = sv[i];
-  }
-  __syncthreads();
-
-  // Pairs that share a counter (normally: the same row) are ordered by (key, bag id); among equal
-  // pairs the arrival order stands, which cannot be told apart in the output.  A pair whose place
-  // changes overwrites what the copy above put there.
-  const int listed = list_n;
-  for (int li = threadIdx.x; li < listed; li += kRankThreads) {
-    const int pos = list[li] & 0xffffu, first = list[li] >> 16;
-    const uint32_t k0 = sk[pos];
-    const int32_t v0 = sv[pos];
-    const uint32_t low = k0 & low_mask;
-    int rank = 0;
-    for (int q = first; q < n; ++q) {
-      const uint32_t kq = sk[q];
-      if ((kq & low_mask) != low) break;
-      const int32_t vq = sv[q];
-      rank += (kq < k0) || (kq == k0 && (vq < v0 || (vq == v0 && q < pos)));
-    }
-    if (first + rank != pos) {
-      kout[first + rank] = k0;
-      vout[first + rank] = v0;
-    }
   }
 }
 
@@ -619,8 +636,9 @@ __global__ void __launch_bounds__(kOversizeThreads) oversize_sort_kernel(uint2* 
   }
 }
 
+int rank_counter_shift(int bits) { return bits > kRankCounterBits ? bits - kRankCounterBits : 0; }
 int rank_words(int bits) {
-  const int w = (1 << bits) / 2;
+  const int w = (1 << (bits - rank_counter_shift(bits))) / 2;  // two 16-bit counters per word
   return w < 32 ? 32 : w;  // whole swizzle groups of 8 chunks
 }
 
@@ -661,17 +679,9 @@ int bucket_sort_plan(const int32_t* indices, const int32_t* offsets, int64_t T, 
   // (key, bag id) pairs between the two levels; keys_in and vals_in are adjacent in the workspace
   uint2* pairs = reinterpret_cast<uint2*>(ws.keys_in);
   const int words = rank_words(g.shift);
-  const int region_words = words > kBucketSortCapacity ? words : kBucketSortCapacity;  // counters, then a list
-  const size_t rank_smem = static_cast<size_t>(region_words) * 4 + static_cast<size_t>(kBucketSortCapacity) * 8;
+  const size_t rank_smem = static_cast<size_t>(words) * 4 + static_cast<size_t>(kBucketSortCapacity) * 8;
   int dev = 0;
   TBE_CUDA_TRY(cudaGetDevice(&dev));
-  static std::atomic<bool> opted_in[64];
-  if (dev < 64 && !opted_in[dev].load(std::memory_order_acquire)) {
-    TBE_CUDA_TRY(cudaFuncSetAttribute(bucket_rank_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (kRankWords > kBucketSortCapacity ? kRankWords : kBucketSortCapacity) * 4 +
-                                          kBucketSortCapacity * 8));
-    opted_in[dev].store(true, std::memory_order_release);
-  }
   const bool wide = g.nb > kFewBuckets;
   constexpr size_t kScatterSmem = kScatterTile * sizeof(uint2) + 3 * kFewBuckets * sizeof(int32_t);
   constexpr size_t kScatterSmemWide = kScatterTileWide * sizeof(uint2) + 3 * kMaxBuckets * sizeof(int32_t);
@@ -706,7 +716,8 @@ int bucket_sort_plan(const int32_t* indices, const int32_t* offsets, int64_t T, 
   {
     KernelTimer timer("bucket_rank_kernel", stream);
     bucket_rank_kernel<<<static_cast<unsigned>(T * g.nb), kRankThreads, rank_smem, stream>>>(
-        ws.bucket_start, pairs, ws.keys, ws.vals, g.shift, words, region_words, queue_count, ws.oversize, qcap);
+        ws.bucket_start, pairs, ws.keys, ws.vals, g.shift, rank_counter_shift(g.shift), words, queue_count, ws.oversize,
+        qcap);
   }
   TBE_CHECK_LAUNCH("bucket_rank_kernel");
   {

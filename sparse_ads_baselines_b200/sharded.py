@@ -237,3 +237,104 @@ class TableShardedEmbeddingBags(nn.Module):
         if self.exchange == "nccl":
             return _NcclExchange.apply(self.tbe(indices, offsets), self.group)
         return _FusedShardedLookup.apply(self.tbe.embedding_weights, self, indices, offsets)
+
+
+# ---------------------------------------------------------------------------- row-wise sharding
+class _FusedRowShardedLookup(torch.autograd.Function):
+    """Lookup over this rank's row slice + reduce-scatter, and all-gather + fused backward, with both
+    exchanges done by peer stores (no collective call)."""
+
+    @staticmethod
+    def forward(ctx, weights, module, indices, offsets):
+        m = module
+        buf = m._buffers_for(indices.device)
+        T, B, D = m.num_tables, m.global_batch, m.embedding_dim
+        W, Bl = buf.world, B // buf.world
+        es = weights.element_size()
+        buf.fwd_step += 1
+        k, slot = buf.fwd_step, buf.fwd_step & 1
+        out = torch.empty((Bl, T, D), dtype=weights.dtype, device=weights.device)
+        with torch.cuda.device(weights.device):
+            stream = tbe_ext._stream(weights.device)
+            buf.sync(_OUT_FREE, k, k - 1, stream)
+            # rank j's staging buffer is [W][B/W][T][D]; this rank fills slot `rank` of every peer's
+            slot_bytes = Bl * T * D * es
+            dst = (ctypes.c_void_p * W)(*[int(p) + buf.rank * slot_bytes for p in buf.out_ptrs[slot]])
+            _lib.call("tbe_forward_sharded", weights.data_ptr(), m.tbe.table_offsets.data_ptr(), indices.data_ptr(),
+                      offsets.data_ptr(), None, dst, W, T, B, D, T, 0, tbe_ext._DTYPES[weights.dtype],
+                      tbe_ext._POOLING["sum"], stream)
+            buf.sync(_OUT_READY, k, k, stream)
+            _lib.call("tbe_reduce_slots", buf.out[slot].data_ptr(), out.data_ptr(), W, Bl * T * D,
+                      tbe_ext._DTYPES[weights.dtype], stream)
+        ctx.module = m
+        ctx.save_for_backward(weights, indices, offsets)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        m = ctx.module
+        weights, indices, offsets = ctx.saved_tensors
+        buf = m._buffers_for(indices.device)
+        grad = grad.contiguous()
+        buf.bwd_step += 1
+        k, slot = buf.bwd_step, buf.bwd_step & 1
+        plan = None
+        if m.tbe.optimizer in (Optimizer.SGD, Optimizer.EXACT_ROWWISE_ADAGRAD):
+            need = tbe_ext._workspace_bytes(indices.numel(), weights.size(0))
+            if buf.plan_workspace is None or buf.plan_workspace.numel() < need:
+                buf.plan_workspace = torch.empty(int(need * 1.1) + 4096, dtype=torch.uint8, device=weights.device)
+            plan = tbe_ext.backward_plan(m.tbe.table_offsets, indices, offsets, weights.size(0),
+                                         workspace=buf.plan_workspace)
+        with torch.cuda.device(weights.device):
+            stream = tbe_ext._stream(weights.device)
+            buf.sync(_GRAD_FREE, k, k - 1, stream)
+            _lib.call("tbe_allgather_push", grad.data_ptr(), buf.grad_ptrs[slot], buf.world, buf.rank,
+                      grad.numel() * grad.element_size(), stream)
+            buf.sync(_GRAD_READY, k, k, stream)
+        m.apply_local_backward(buf.grad_in[slot], indices, offsets, plan=plan)
+        return None, None, None, None
+
+
+class _NcclRowExchange(torch.autograd.Function):
+    """Reduce-scatter forward, all-gather backward: ReduceScatterFunction of the reference
+    (sparse_embedding_cuda_ops.py:78-85) on torch.distributed."""
+
+    @staticmethod
+    def forward(ctx, partial, group):
+        ctx.group = group
+        W = dist.get_world_size(group)
+        out = torch.empty((partial.shape[0] // W,) + tuple(partial.shape[1:]), dtype=partial.dtype, device=partial.device)
+        dist.reduce_scatter_tensor(out, partial.contiguous(), group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        W = dist.get_world_size(ctx.group)
+        full = torch.empty((grad.shape[0] * W,) + tuple(grad.shape[1:]), dtype=grad.dtype, device=grad.device)
+        dist.all_gather_into_tensor(full, grad.contiguous(), group=ctx.group)
+        return full, None
+
+
+class RowShardedEmbeddingBags(TableShardedEmbeddingBags):
+    """Row-wise sharding: every rank holds ``rows_per_rank`` rows of each of ``num_tables`` tables
+    (the reference's ``DistributedUniformShardedSNN``, models.py:194-209) and looks up the GLOBAL
+    batch with indices local to its slice; ``forward`` returns this rank's batch slice
+    ``[B/W, T, D]`` of the sum over ranks (reduce-scatter), ``backward`` all-gathers the gradient
+    and applies the fused optimizer to the local rows.  ``exchange="fused"``: the lookup kernel
+    stores its partial rows straight into the owner's staging slot and one local kernel sums the
+    slots; ``exchange="nccl"``: library reduce-scatter / all-gather.  Sum pooling only (a mean over
+    a bag needs the bag's global length, which no single rank sees)."""
+
+    def __init__(self, num_tables, rows_per_rank, embedding_dim, global_batch, optimizer=Optimizer.SGD,
+                 learning_rate=0.01, eps=None, fp16=False, exchange="fused", group=None, sync_timeout_s=30.0):
+        super().__init__(num_tables, rows_per_rank, embedding_dim, global_batch, optimizer=optimizer,
+                         learning_rate=learning_rate, eps=eps, fp16=fp16, pooling_mode="sum", exchange=exchange,
+                         group=group, sync_timeout_s=sync_timeout_s)
+        self.num_tables = num_tables
+
+    def forward(self, indices, offsets):
+        if self.world == 1:
+            return self.tbe(indices, offsets)
+        if self.exchange == "nccl":
+            return _NcclRowExchange.apply(self.tbe(indices, offsets), self.group)
+        return _FusedRowShardedLookup.apply(self.tbe.embedding_weights, self, indices, offsets)

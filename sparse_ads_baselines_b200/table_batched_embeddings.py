@@ -319,17 +319,18 @@ def backward_approx_adagrad(grad_output, weights, table_offsets, indices, offset
 # columns of the [B, sum(D)] output (tbe_forward_strided) / are read from its columns of the
 # gradient (strided backward), so nothing is copied.
 
-_host_copies = {}
-
-
 def _host_list(t):
-    key = (t.data_ptr(), t.numel(), t._version)
-    v = _host_copies.get(key)
-    if v is None:
-        if len(_host_copies) > 256:
-            _host_copies.clear()
-        v = [int(x) for x in t.detach().cpu().tolist()]
-        _host_copies[key] = v
+    """Host copy of a small index tensor, kept on the tensor object (per version): one
+    synchronisation per distinct tensor, and no confusion when the allocator reuses an address."""
+    cached = getattr(t, "_tbe_host_list", None)
+    key = (t._version, t.numel())
+    if cached is not None and cached[0] == key:
+        return cached[1]
+    v = [int(x) for x in t.detach().cpu().tolist()]
+    try:
+        t._tbe_host_list = (key, v)
+    except AttributeError:
+        pass
     return v
 
 
@@ -369,18 +370,39 @@ def _mixed_tables(weights, table_offsets, dim_offsets, indices, offsets):
 
 def forward_mixed_D(weights, table_offsets, dim_offsets, total_D, indices, offsets, indice_weights, L_max,
                     BT_block_size, shmem):
-    """Pooled lookup over tables of different width: returns ``[B, total_D]`` (reference:
-    batched_embedding_forward_mixed_D_cuda, table_batched_embeddings_cuda.cu:945-1004)."""
-    tables, B, T = _mixed_tables(weights, table_offsets, dim_offsets, indices, offsets)
-    dev = weights.device
-    out = torch.empty((B, int(total_D)), dtype=weights.dtype, device=dev)
+    """Pooled lookup over tables of different width in one launch: returns ``[B, total_D]``
+    (reference: batched_embedding_forward_mixed_D_cuda, table_batched_embeddings_cuda.cu:945-1004).
+    ``table_offsets`` are int64 element offsets ``[T+1]`` into the flat ``weights``, ``dim_offsets``
+    int32 output columns ``[T+1]``, as MixedDimTableBatchedEmbeddingBags registers them."""
+    _check_cuda("weights", weights)
+    _require(weights.dim() == 1 and weights.is_contiguous(), "mixed-D weights must be a flat contiguous vector")
+    _require(weights.dtype in _DTYPES, "weights must be float16, float32 or float64")
+    _check_cuda("table_offsets", table_offsets, torch.int64)
+    _check_cuda("dim_offsets", dim_offsets, torch.int32)
+    _check_cuda("indices", indices, torch.int32)
+    _check_cuda("offsets", offsets, torch.int32)
+    elem, cols = _host_list(table_offsets), _host_list(dim_offsets)  # host copies, cached per tensor
+    T = len(cols) - 1
+    _require(len(elem) == T + 1, "table_offsets and dim_offsets must both have T + 1 entries")
+    _require((offsets.numel() - 1) % T == 0, "offsets must have T*B+1 entries")
+    B = (offsets.numel() - 1) // T
+    _require(B > 0, "batch size must be > 0")
+    dims = [cols[t + 1] - cols[t] for t in range(T)]
+    _require(all(d > 0 and d % 4 == 0 for d in dims), "every embedding dimension must be a positive multiple of 4")
+    _require(int(total_D) == cols[-1], "total_D must equal dim_offsets[-1]")
     es = weights.element_size()
+    vb = 16 if all((d * es) % 16 == 0 for d in dims) and all((e * es) % 16 == 0 for e in elem) else 8
+    dev = weights.device
+    psw = None
+    if indice_weights is not None:
+        _check_cuda("indice_weights", indice_weights, weights.dtype)
+        _require(indice_weights.numel() == indices.numel(), "indice_weights must have one entry per index")
+        psw = indice_weights.contiguous()
     with torch.cuda.device(dev):
-        for (t, w_t, idx_t, off_t, lo, hi, col0, D) in tables:
-            psw = indice_weights[lo:hi].contiguous() if indice_weights is not None else None
-            _lib.call("tbe_forward_strided", w_t.data_ptr(), _one_table_offsets(dev).data_ptr(), idx_t.data_ptr(),
-                      off_t.data_ptr(), psw.data_ptr() if psw is not None else None, out.data_ptr() + col0 * es,
-                      int(total_D), 1, B, D, _DTYPES[weights.dtype], _POOLING["sum"], _stream(dev))
+        out = torch.empty((B, int(total_D)), dtype=weights.dtype, device=dev)
+        _lib.call("tbe_forward_mixed", weights.data_ptr(), table_offsets.data_ptr(), dim_offsets.data_ptr(),
+                  indices.data_ptr(), offsets.data_ptr(), psw.data_ptr() if psw is not None else None, out.data_ptr(),
+                  T, B, int(total_D), _DTYPES[weights.dtype], vb, _stream(dev))
     return out
 
 

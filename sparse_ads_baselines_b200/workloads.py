@@ -58,6 +58,7 @@ WORKLOADS = {
     "prof_cfg3": Workload("prof_cfg3", T=8, E=1_000_000, D=128, B=2048, dtype="fp32", pooling="mean",
                           optimizer="exact_rowwise_adagrad", lr=0.01, eps=1e-8, L_dist="poisson", L_mean=20.0,
                           L_min=1, L_max=100, index_dist="zipf", zipf_alpha=1.05),
+    "prof_cfg5": Workload("prof_cfg5", T=8, E=1_000_000, D=128, B=65_536, dtype="fp16", L=32, optimizer="sgd", lr=0.05),
     # the headline target: cfg2's shapes with forward + backward + fused exact SGD
     "target": Workload("target", T=64, E=1_000_000, D=128, B=2048, dtype="fp16", L=38, optimizer="sgd", lr=0.05),
 }

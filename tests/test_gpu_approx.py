@@ -64,6 +64,27 @@ def test_approx_adagrad_repeated_rows_are_applied_in_index_order(cuda_device, dt
     assert torch.equal(w1, w2) and torch.equal(s1, s2)
 
 
+@pytest.mark.parametrize("dtype,D", [(torch.float32, 32), (torch.float16, 128), (torch.float32, 68)])
+@pytest.mark.parametrize("T,E,B,L", [(2, 6, 300, 3), (3, 40, 64, 9), (1, 2, 700, 1)])
+def test_approx_adagrad_hot_rows(cuda_device, dtype, D, T, E, B, L):
+    """Rows with hundreds of lookups: runs that cross the 32-entry tiles and runs long enough for the
+    CTA-per-run kernel.  The per-lookup state sequence (a prefix sum on the device) and the weighted
+    sum of gradient rows must give the oracle's one-lookup-at-a-time result, deterministically."""
+    c = to_device(make_case(T=T, E=E, D=D, B=B, Lmax=L, dtype=dtype, seed=D + B, fixed_L=L), cuda_device)
+    c["grad_d"] = c["grad_d"] * 0.1
+    c["grad"] = c["grad_d"].cpu()
+    s0 = torch.rand(T * E, device=cuda_device) * 0.5
+    w1, s1, _ = _approx(c, s0, 0.05, 0.1, False)
+    rw, rs, _ = oracle.approx_rowwise_adagrad_step(c["weights"], s0.cpu(), c["table_offsets"], c["indices"],
+                                                   c["offsets"], c["grad"], 0.05, 0.1)
+    torch.testing.assert_close(s1.cpu(), rs, rtol=1e-3 if dtype == torch.float16 else 1e-5, atol=1e-5)
+    # hundreds of terms per row, summed in another order than the oracle's: absolute 1e-5 in fp32
+    tol = dict(rtol=1e-2, atol=1e-2) if dtype == torch.float16 else dict(rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(w1.float().cpu(), rw.float(), **tol)
+    w2, s2, _ = _approx(c, s0, 0.05, 0.1, False)
+    assert torch.equal(w1, w2) and torch.equal(s1, s2)
+
+
 def test_approx_golden(cuda_device):
     z = np.load(os.path.join(GOLDEN, "tiny_fp32_weighted_approx.npz"))
     T, E = int(z["T"]), int(z["E"])

@@ -90,6 +90,19 @@ def test_cached_module_is_transparent(cuda_device, fp16, pooling):
                                **tol)
 
 
+def test_empty_batch_clears_every_counter(cuda_device):
+    """A step without lookups after a step with uncached rows reports zeros in all five counters."""
+    T, E, D, B = 2, 40, 8, 4
+    m = LXUCachedEmbeddingBags(T, E, D, cache_rows=4, ways=1, policy="lru", learning_rate=0.0)
+    rng = np.random.default_rng(1)
+    idx, off = _batch(rng, T, E, B, 6)
+    m(torch.from_numpy(idx).cuda(), torch.from_numpy(off).cuda())
+    assert m.last_stats()["uncached"] > 0
+    m(torch.zeros(0, dtype=torch.int32, device="cuda"), torch.zeros(T * B + 1, dtype=torch.int32, device="cuda"))
+    got = m.last_stats()
+    assert all(got[k] == 0 for k in ("lookups", "rows", "fetched", "hit_lookups", "hit_rows", "uncached")), got
+
+
 def test_hit_rate_grows_with_reuse(cuda_device):
     """Zipf lookups through a cache larger than the hot set: after a few steps most lookups hit."""
     T, E, D, B, L = 4, 5000, 16, 64, 20

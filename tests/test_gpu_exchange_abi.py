@@ -165,3 +165,74 @@ def test_nccl_path_transposed_gradient_view(cuda_device):
     torch.cuda.synchronize()
     expect = oracle.sgd_step(w, [0, E], idx, off, view.contiguous(), lr)
     torch.testing.assert_close(wd.cpu(), expect, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_row_sharded_exchange_one_gpu(cuda_device, world, dtype):
+    """Row-wise sharding: every emulated rank looks up the global batch over its own row slice and
+    stores the partial rows into slot `rank` of the owners' staging buffers (tbe_forward_sharded with
+    advanced pointers); tbe_reduce_slots sums the slots; tbe_allgather_push gathers the gradient."""
+    dev = cuda_device
+    T, E, D, Bl, Lmax = 3, 40, 64, 4, 6
+    B = Bl * world
+    cases = [_rank_case(50 + r, T, E, D, B, Lmax, dtype) for r in range(world)]  # (indices, offsets, row slice)
+    es = 2 if dtype == torch.float16 else 4
+    stage = [torch.full((world, Bl, T, D), float("nan"), dtype=dtype, device=dev) for _ in range(world)]
+    to = (torch.arange(T, dtype=torch.int32) * E).to(dev)
+    for r, (idx, off, w) in enumerate(cases):
+        wd, idx_d, off_d = w.to(dev), torch.from_numpy(idx).to(dev), torch.from_numpy(off).to(dev)
+        dst = (ctypes.c_void_p * world)(*[s_.data_ptr() + r * Bl * T * D * es for s_ in stage])
+        _lib.call("tbe_forward_sharded", wd.data_ptr(), to.data_ptr(), idx_d.data_ptr(), off_d.data_ptr(), None, dst,
+                  world, T, B, D, T, 0, _dt(dtype), _lib.TBE_POOL_SUM, _stream(dev))
+    outs = []
+    for j in range(world):
+        out = torch.empty(Bl, T, D, dtype=dtype, device=dev)
+        _lib.call("tbe_reduce_slots", stage[j].data_ptr(), out.data_ptr(), world, Bl * T * D, _dt(dtype), _stream(dev))
+        outs.append(out)
+    torch.cuda.synchronize()
+    to_h = [t * E for t in range(T)]
+    partial = [oracle.forward(w, to_h, i, o, compute_dtype=torch.float32) for (i, o, w) in cases]
+    expect = oracle.reduce_scatter_pooled(partial)
+    for j in range(world):
+        assert not torch.isnan(stage[j].float()).any()
+        torch.testing.assert_close(outs[j].cpu().float(), expect[j].float(), **TOL[dtype])
+    # the gradient slices, gathered on every rank
+    g = torch.Generator().manual_seed(9)
+    grads = [torch.randn(Bl, T, D, generator=g).to(dtype) for _ in range(world)]
+    gathered = [torch.full((B, T, D), float("nan"), dtype=dtype, device=dev) for _ in range(world)]
+    for j in range(world):
+        src = grads[j].to(dev)
+        _lib.call("tbe_allgather_push", src.data_ptr(), _ptrs(gathered), world, j, src.numel() * es, _stream(dev))
+    torch.cuda.synchronize()
+    expect_g = oracle.all_gather_pooled_backward(grads)
+    for r in range(world):
+        assert torch.equal(gathered[r].cpu(), expect_g[r])
+
+
+@pytest.mark.parametrize("world,Tl,Bl,Lmax", [(2, 3, 4, 5), (4, 1, 7, 40), (8, 2, 3, 0), (3, 5, 64, 70)])
+def test_regroup_bags_matches_oracle(cuda_device, world, Tl, Bl, Lmax):
+    """Phase 3 of the index all-to-all: the [W][T/W][B/W] bags a rank received, regrouped to
+    [T/W][B] order by tbe_permute_bags, equal the oracle's index all-to-all for that rank."""
+    from sparse_ads_baselines_b200 import input_pipeline
+    T = Tl * world
+    feats = []
+    for r in range(world):
+        rng = np.random.default_rng(700 + r)
+        lens = rng.integers(0, Lmax + 1, size=T * Bl)
+        off = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+        feats.append((rng.integers(0, 10 ** 6, size=int(off[-1])).astype(np.int32), off))
+    want = oracle.index_all_to_all([f[0] for f in feats], [f[1] for f in feats], T)
+    for r in range(world):
+        # what rank r receives: from every rank j, the [Tl][Bl] bags of r's tables, table-major
+        blocks, lens = [], []
+        for j in range(world):
+            off = feats[j][1].astype(np.int64)
+            lo, hi = off[r * Tl * Bl], off[(r + 1) * Tl * Bl]
+            blocks.append(feats[j][0][lo:hi])
+            lens.append(np.diff(off[r * Tl * Bl:(r + 1) * Tl * Bl + 1]))
+        recv_idx = torch.from_numpy(np.concatenate(blocks).astype(np.int32)).to(cuda_device)
+        recv_len = torch.from_numpy(np.stack(lens).astype(np.int32).reshape(world, Tl, Bl)).to(cuda_device)
+        idx, off = input_pipeline.regroup_bags(recv_idx, recv_len)
+        assert np.array_equal(off.cpu().numpy(), want[r][1])
+        assert np.array_equal(idx.cpu().numpy(), want[r][0])

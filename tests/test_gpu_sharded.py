@@ -89,6 +89,45 @@ def _worker(rank, world, port, exchange, dtype_name, failures):
             for _ in range(3):
                 o = m(idx_d, off_d)
         m.check_exchange()
+        # row-wise sharding on the same ranks: every rank holds E rows of each of Tl tables and looks
+        # up the global batch with indices local to its slice; reduce-scatter forward, all-gather backward
+        from sparse_ads_baselines_b200.sharded import RowShardedEmbeddingBags
+        rcases = [_rank_case(500 + r, Tl, E, D, B, Lmax, dtype) for r in range(world)]
+        partial = [oracle.forward(w_, to, i_, o_, compute_dtype=torch.float32) for (i_, o_, w_) in rcases]
+        r_expect = oracle.reduce_scatter_pooled(partial)[rank]
+        g3 = torch.Generator().manual_seed(70)
+        rgrads = [torch.randn(B // world, Tl, D, generator=g3).to(dtype) for _ in range(world)]
+        r_gin = oracle.all_gather_pooled_backward(rgrads)[rank]
+        ridx, roff, rw0 = rcases[rank]
+        r_expect_w = oracle.sgd_step(rw0, to, ridx, roff, r_gin, lr, compute_dtype=torch.float32)
+        rm = RowShardedEmbeddingBags(Tl, E, D, B, optimizer=ops.Optimizer.SGD, learning_rate=lr,
+                                     fp16=(dtype == torch.float16), exchange=exchange).to(dev)
+        ridx_d, roff_d = torch.from_numpy(ridx).to(dev), torch.from_numpy(roff).to(dev)
+        for step in range(2):
+            rm.tbe.embedding_weights.data.copy_(rw0.to(dev))
+            rout = rm(ridx_d, roff_d)
+            assert tuple(rout.shape) == (B // world, Tl, D)
+            torch.testing.assert_close(rout.detach().float().cpu(), r_expect.float(), **tol)
+            rout.backward(rgrads[rank].to(dev))
+            torch.cuda.synchronize()
+            torch.testing.assert_close(rm.tbe.embedding_weights.detach().float().cpu(), r_expect_w.float(), **tol)
+        rm.check_exchange()
+        if exchange == "fused" and dtype_name == "fp32":
+            # the index all-to-all in front of the lookup: data-parallel features in, my tables' out
+            from sparse_ads_baselines_b200 import input_pipeline
+            T_all, Bl_ = Tl * world, B // world
+            feats = []
+            for r in range(world):
+                rng = np.random.default_rng(800 + r)
+                lens = rng.integers(0, Lmax + 1, size=T_all * Bl_)
+                off_r = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+                feats.append((rng.integers(0, E, size=int(off_r[-1])).astype(np.int32), off_r))
+            got_idx, got_off = input_pipeline.indices_all_to_all(torch.from_numpy(feats[rank][0]).to(dev),
+                                                                 torch.from_numpy(feats[rank][1]).to(dev), T_all)
+            want_idx, want_off = oracle.index_all_to_all([f[0] for f in feats], [f[1] for f in feats], T_all)[rank]
+            assert np.array_equal(got_off.cpu().numpy(), want_off) and np.array_equal(got_idx.cpu().numpy(), want_idx)
+            out_p = m(got_idx, got_off)  # and the exchanged features drive the sharded lookup
+            assert tuple(out_p.shape) == (B // world, Tl * world, D)
         if exchange == "nccl" and dtype_name == "fp32":
             # row-wise sharding collectives, after test_sparse_embedding_cuda.py:138-171: the same seed
             # on every rank regenerates every rank's tensor

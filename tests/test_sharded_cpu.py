@@ -47,6 +47,40 @@ def _worker(rank, world, port, B, Tl, D, failures):
         y = sharded._NcclExchange.apply(x, None)
         y.backward(grads[rank])
         assert torch.equal(x.grad, expect_b), "autograd of the exchange"
+        # row-wise sharding: reduce-scatter forward, all-gather backward (test_sparse_embedding_cuda.py:138-171)
+        parts = [_rank_inputs(200 + r, B, Tl, D) for r in range(world)]
+        xr = parts[rank].clone().requires_grad_(True)
+        yr = sharded._NcclRowExchange.apply(xr, None)
+        torch.testing.assert_close(yr.detach(), oracle.reduce_scatter_pooled(parts)[rank], rtol=1e-6, atol=1e-6)
+        gr = [_rank_inputs(300 + r, B // world, Tl, D) for r in range(world)]
+        yr.backward(gr[rank])
+        assert torch.equal(xr.grad, oracle.all_gather_pooled_backward(gr)[rank]), "all-gather of the gradient"
+        # index all-to-all (phases 1-2 on CPU tensors): data-parallel features -> my tables' features
+        import numpy as np
+        from sparse_ads_baselines_b200 import input_pipeline
+        T_all, Bl_, Lmax = 2 * world, 3, 4
+        feats = []
+        for r in range(world):
+            rng = np.random.default_rng(900 + r)
+            lens = rng.integers(0, Lmax + 1, size=T_all * Bl_)
+            off = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+            feats.append((rng.integers(0, 1000, size=int(off[-1])).astype(np.int32), off))
+        recv_idx, recv_len = input_pipeline.exchange_indices(torch.from_numpy(feats[rank][0]), torch.from_numpy(feats[rank][1]),
+                                                              T_all)
+        Tl_ = T_all // world
+        assert tuple(recv_len.shape) == (world, Tl_, Bl_)
+        # regroup on the host the way tbe_permute_bags does on the device
+        src_off = np.concatenate([[0], np.cumsum(recv_len.numpy().reshape(-1))])
+        pieces, lens_out = [], []
+        for t in range(Tl_):
+            for j in range(world):
+                for b in range(Bl_):
+                    sb = (j * Tl_ + t) * Bl_ + b
+                    pieces.append(recv_idx.numpy()[src_off[sb]:src_off[sb + 1]])
+                    lens_out.append(src_off[sb + 1] - src_off[sb])
+        want_idx, want_off = oracle.index_all_to_all([f[0] for f in feats], [f[1] for f in feats], T_all)[rank]
+        assert np.array_equal(np.concatenate(pieces) if pieces else np.zeros(0), want_idx), "index all-to-all"
+        assert np.array_equal(np.concatenate([[0], np.cumsum(lens_out)]), want_off), "offsets after the index all-to-all"
         # B not divisible by the world size is refused (sparse_embedding_cuda.cpp:500)
         try:
             sharded.pooled_all_to_all(torch.zeros(B + 1, Tl, D))
