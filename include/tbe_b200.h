@@ -67,7 +67,8 @@ TBE_API int64_t tbe_library_launch_count(void);
  *   bwd_vpl, bwd_unroll                          backward apply: 16-byte vectors per lane (1/2/4), runs in flight (1/2)
  *   long_segment                                 run length above which a run gets a CTA of its own
  *   bwd_sort                                     1: always linearize + device radix sort for the backward plan
- *   sort_bucket                                  wanted mean bucket size of the table-segmented sort */
+ *   sort_bucket                                  wanted mean bucket size of the table-segmented sort
+ *   split_runs                                   1: one CTA per queued long run, never several */
 TBE_API int tbe_set_tuning(const char* name, int value);
 
 /* Per-launch timing for benchmarks: while enabled, every kernel launch of this library
@@ -231,8 +232,11 @@ TBE_API int tbe_backward_exact_rowwise_adagrad(
  * device memory: a host that binds this ABI through a bare FFI and has no device allocator of
  * its own, or a serving process whose HBM is fully budgeted at start-up and which must not
  * call cudaMalloc (a device-wide synchronisation) while handling a request.  The scratch is
- * a fixed array inside the library's device image (tbe_noalloc_scratch_bytes() bytes, held
- * by every GPU that loads the library until the process exits); the call allocates nothing.
+ * a fixed array inside the library's device image (tbe_noalloc_scratch_bytes() bytes, held by
+ * every GPU that has used this entry point until the process exits); the call itself allocates
+ * nothing, but CUDA loads a library's device image lazily, so the array takes its place in device
+ * memory during the FIRST call on a device: make one warm-up call per device at start-up, while
+ * memory is still available, not on the first request.
  * Same arguments and results as tbe_backward_sgd without plan_ready / workspace.
  *  - Limit: N <= TBE_NOALLOC_MAX_LOOKUPS; larger batches are rejected with
  *    TBE_ERR_WORKSPACE_TOO_SMALL and a message naming the limit.

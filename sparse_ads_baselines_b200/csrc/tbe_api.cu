@@ -19,7 +19,7 @@ std::atomic<int64_t> g_library_launches{0};
 std::atomic<int> g_tuning[kTuneCount];
 const char* const kTuningNames[kTuneCount] = {"fwd_unroll", "fwd_threads", "bwd_threads", "bwd_unroll",
                                               "long_segment", "fwd_blocks_per_sm", "bwd_blocks_per_sm", "bwd_vpl",
-                                              "bwd_sort", "sort_bucket"};
+                                              "bwd_sort", "sort_bucket", "split_runs"};
 }  // namespace
 
 namespace {

@@ -163,6 +163,7 @@ namespace {
 enum Opt { kSGD = 0, kExactAdagrad = 1, kApproxAdagrad = 2 };
 
 constexpr int kDefaultLongSegment = 64;
+constexpr int kMinSplitPart = 256;  // entries per part of a split long run (doubled until the scratch fits)
 constexpr int kBwdThreads = 256;
 
 // ------------------------------------------------------------------ step 1: linearize
@@ -237,7 +238,30 @@ struct BwdArgs {
   float lr, eps;
   uint64_t sr_seed, sr_offset;
   const float* bag_g2;       // approximate Adagrad: squared gradient norm of every bag
+  // long runs cut into parts (0 = off): a part is split_len entries (the last one up to twice that)
+  int32_t split_len, max_parts;
+  int4* part_list;           // dense list of parts: {first entry, end entry, list index of the run's first part, parts of the run}
+  int32_t* part_count;       // parts listed so far
+  int32_t* part_tickets;     // at the list index of a run's first part: parts of the run finished so far
+  float* part_sums;          // [max_parts][D] partial sums, one slot per listed part
 };
+
+// Queues a run of sorted entries [s, e) that is too long for the lane groups of run_kernel; called by the
+// first lane of the group that found it.  A run of at least two parts is also cut into parts: they take
+// consecutive places in the part list, and the ticket of the run starts at zero.
+__device__ __forceinline__ void enqueue_long_run(const BwdArgs& a, int s, int e) {
+  a.long_list[atomicAdd(a.long_count, 1)] = make_int2(s, e);
+  const int part = a.split_len;
+  if (part > 0 && e - s >= 2 * part) {
+    const int nparts = (e - s) / part;
+    const int base = atomicAdd(a.part_count, nparts);  // at most N / split_len parts exist in total
+    a.part_tickets[base] = 0;
+    for (int k = 0; k < nparts; ++k) {
+      const int ps = s + k * part;
+      a.part_list[base + k] = make_int4(ps, k == nparts - 1 ? e : ps + part, base, nparts);
+    }
+  }
+}
 
 // Step size of approximate rowwise Adagrad after the state has reached s.
 __device__ __forceinline__ float approx_step(const BwdArgs& a, float s) { return a.lr * (1.0f / (sqrtf(s) + a.eps)); }
@@ -510,7 +534,7 @@ __global__ void __launch_bounds__(kBwdThreads, 4) run_kernel(const BwdArgs a) {
           tail_lo[q] = p0 + 32;
           tail_hi[q] = run_end(keys, tail_lo[q] + 1, N, after);
           if (len[q] + (tail_hi[q] - tail_lo[q]) > a.long_threshold) {
-            if (sub == 0) a.long_list[atomicAdd(a.long_count, 1)] = make_int2(p0 + i, tail_hi[q]);
+            if (sub == 0) enqueue_long_run(a, p0 + i, tail_hi[q]);
             has[q] = false;
             len[q] = 0;
             tail_hi[q] = tail_lo[q];
@@ -695,7 +719,7 @@ __global__ void __launch_bounds__(kBwdThreads) run_kernel_wide(const BwdArgs a) 
         tail_lo = p0 + 32;
         tail_hi = run_end(keys, tail_lo + 1, N, row);
         if (len + (tail_hi - tail_lo) > a.long_threshold) {
-          if (sub == 0) a.long_list[atomicAdd(a.long_count, 1)] = make_int2(p0 + i, tail_hi);
+          if (sub == 0) enqueue_long_run(a, p0 + i, tail_hi);
           has = false;
           len = 0;
           tail_hi = tail_lo;
@@ -766,7 +790,13 @@ __global__ void __launch_bounds__(kBwdThreads) run_kernel_wide(const BwdArgs a) 
   }
 }
 
-// One CTA per queued long run.
+// Queued long runs.  A run shorter than two parts (a.split_len entries each) gets one CTA, which sums
+// it and applies the update.  A longer run -- a hot row with thousands of lookups -- would make one
+// CTA the critical path of the whole kernel, so the lane group that queued it also cut it into parts
+// (part_list): every part is summed by whichever CTA picks it and left as an fp32 partial sum,
+// and the CTA that finishes a run's LAST outstanding part (a ticket per run) adds the partial sums in
+// part order and applies the update.  The order of every summation is fixed by the sorted order and
+// the part boundaries, never by scheduling.
 template <typename T, int VB, int OPT, bool MEAN, bool SR>
 __global__ void __launch_bounds__(kBwdThreads) long_run_kernel(const BwdArgs a) {
   using acc_t = typename Acc<T>::type;
@@ -778,6 +808,7 @@ __global__ void __launch_bounds__(kBwdThreads) long_run_kernel(const BwdArgs a) 
   __shared__ acc_t part[kBwdThreads * NE];
   __shared__ int64_t entry_off[kBwdThreads];   // byte offset of the gradient row of an entry
   __shared__ acc_t entry_scale[kBwdThreads];   // 1/L of its bag (mean pooling)
+  __shared__ int ticket;                       // parts of a split run finished before this CTA's
   const int lane = threadIdx.x & 31;
   const int lpr_log2 = a.lpr1_log2;
   const int lpr = 1 << lpr_log2;
@@ -789,96 +820,94 @@ __global__ void __launch_bounds__(kBwdThreads) long_run_kernel(const BwdArgs a) 
   Philox rng(a.sr_seed, (1ull << 40) + static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x, a.sr_offset);
   const uint64_t keep = l2_policy_evict_last(), streaming = l2_policy_evict_first();
 
-  for (int li = blockIdx.x; li < nlong; li += gridDim.x) {
-    const int2 run = a.long_list[li];
-    const int s = run.x, len = run.y - run.x;
-    const uint32_t row = key_to_row(a.table_offsets, a.idx_bits, __ldg(a.keys + s));
-    char* wrow = static_cast<char*>(a.weights) + static_cast<int64_t>(row) * row_bytes;
-    const float st_first = APPROX ? a.state[row] : 0.f;  // read by every thread before thread 0 overwrites it
-
-    // Folds the groups' partial sums for chunk c in group order; every thread of warp 0 ends with the
-    // total of its own `sub`.  The run is taken 256 entries at a time: every thread first turns one
-    // entry's bag id into the offset of its gradient row (and 1/L for mean pooling) and leaves it in
-    // shared memory, then group g sums entries g, g + groups, ... with eight row loads in flight and
-    // no load depending on another.
-    auto reduce_chunk = [&](int c, acc_t* total) {
-      const int v = (c << 5) + sub;
-      const bool vact = v < a.nvec;
-      acc_t acc[NE];
+  // Sums chunk c of the gradient rows of sorted entries [s, s + len):
+  // Folds the groups' partial sums for chunk c in group order; every thread of warp 0 ends with the
+  // total of its own `sub`.  The run is taken 256 entries at a time: every thread first turns one
+  // entry's bag id into the offset of its gradient row (and 1/L for mean pooling) and leaves it in
+  // shared memory, then group g sums entries g, g + groups, ... with eight row loads in flight and
+  // no load depending on another.
+  auto reduce_range = [&](int c, int s, int len, float st_first, acc_t* total) {
+    const int v = (c << 5) + sub;
+    const bool vact = v < a.nvec;
+    acc_t acc[NE];
 #pragma unroll
-      for (int k = 0; k < NE; ++k) acc[k] = 0;
-      if (APPROX && threadIdx.x == 0) carry = st_first;
-      for (int base = 0; base < len; base += kBwdThreads) {
-        const int m = min(kBwdThreads, len - base);
-        __syncthreads();  // the previous block of entries has been consumed
-        float g2 = 0.f;
-        if (static_cast<int>(threadIdx.x) < m) {
-          const uint32_t bag = static_cast<uint32_t>(__ldg(a.vals + s + base + threadIdx.x));
-          if (APPROX) g2 = __ldg(a.bag_g2 + bag);
-          const uint32_t t = fastdiv(bag, a.divB);
-          const uint32_t b = bag - t * static_cast<uint32_t>(a.B);
-          entry_off[threadIdx.x] = (static_cast<int64_t>(b) * a.stride_b + static_cast<int64_t>(t) * a.stride_t) *
-                                   static_cast<int64_t>(sizeof(T));
-          if (MEAN)
-            entry_scale[threadIdx.x] =
-                acc_t(1) / static_cast<acc_t>(__ldg(a.offsets + bag + 1) - __ldg(a.offsets + bag));
-        }
-        if (APPROX) {
-          // state after every entry = state so far + inclusive prefix sum of g2 over the block, in a
-          // fixed order: shuffles inside a warp, then the totals of the warps in front
-          float incl = g2;
+    for (int k = 0; k < NE; ++k) acc[k] = 0;
+    if (APPROX && threadIdx.x == 0) carry = st_first;
+    for (int base = 0; base < len; base += kBwdThreads) {
+      const int m = min(kBwdThreads, len - base);
+      __syncthreads();  // the previous block of entries has been consumed
+      float g2 = 0.f;
+      if (static_cast<int>(threadIdx.x) < m) {
+        const uint32_t bag = static_cast<uint32_t>(__ldg(a.vals + s + base + threadIdx.x));
+        if (APPROX) g2 = __ldg(a.bag_g2 + bag);
+        const uint32_t t = fastdiv(bag, a.divB);
+        const uint32_t b = bag - t * static_cast<uint32_t>(a.B);
+        entry_off[threadIdx.x] = (static_cast<int64_t>(b) * a.stride_b + static_cast<int64_t>(t) * a.stride_t) *
+                                 static_cast<int64_t>(sizeof(T));
+        if (MEAN)
+          entry_scale[threadIdx.x] =
+              acc_t(1) / static_cast<acc_t>(__ldg(a.offsets + bag + 1) - __ldg(a.offsets + bag));
+      }
+      if (APPROX) {
+        // state after every entry = state so far + inclusive prefix sum of g2 over the block, in a
+        // fixed order: shuffles inside a warp, then the totals of the warps in front
+        float incl = g2;
 #pragma unroll
-          for (int o = 1; o < 32; o <<= 1) {
-            const float up = __shfl_up_sync(kFullMask, incl, o);
-            if (lane >= o) incl += up;
-          }
-          if (lane == 31) scan_tot[threadIdx.x >> 5] = incl;
-          __syncthreads();
-          float before = carry;
-          for (int w2 = 0; w2 < static_cast<int>(threadIdx.x >> 5); ++w2) before += scan_tot[w2];
-          const float st = before + incl;
-          entry_scale[threadIdx.x] = static_cast<acc_t>(approx_step(a, st));
-          __syncthreads();  // everyone has read `carry`
-          if (threadIdx.x == blockDim.x - 1) carry = st;
+        for (int o = 1; o < 32; o <<= 1) {
+          const float up = __shfl_up_sync(kFullMask, incl, o);
+          if (lane >= o) incl += up;
         }
+        if (lane == 31) scan_tot[threadIdx.x >> 5] = incl;
         __syncthreads();
-        for (int i = gid; i < m; i += groups * 8) {
-          Raw<VB> r[8];
-          acc_t sc[8];
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const int iu = i + u * groups;
-            r[u] = raw_zero<VB>();
-            sc[u] = 1;
-            if (iu < m && vact) {
-              r[u] = ld_stream_hint<VB>(static_cast<const char*>(a.grad) + entry_off[iu] + static_cast<int64_t>(v) * VB,
-                                        keep);
-              if (SCALED) sc[u] = entry_scale[iu];
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < 8; ++u) add_grad<T, VB, SCALED>(r[u], sc[u], acc);
-        }
+        float before = carry;
+        for (int w2 = 0; w2 < static_cast<int>(threadIdx.x >> 5); ++w2) before += scan_tot[w2];
+        const float st = before + incl;
+        entry_scale[threadIdx.x] = static_cast<acc_t>(approx_step(a, st));
+        __syncthreads();  // everyone has read `carry`
+        if (threadIdx.x == blockDim.x - 1) carry = st;
       }
-      __syncthreads();  // previous use of `part` finished
-#pragma unroll
-      for (int k = 0; k < NE; ++k) part[threadIdx.x * NE + k] = acc[k];
       __syncthreads();
+      for (int i = gid; i < m; i += groups * 8) {
+        Raw<VB> r[8];
+        acc_t sc[8];
 #pragma unroll
-      for (int k = 0; k < NE; ++k) total[k] = 0;
-      if (threadIdx.x < 32) {
-        for (int g = 0; g < groups; ++g) {
-#pragma unroll
-          for (int k = 0; k < NE; ++k) total[k] += part[(g * lpr + sub) * NE + k];
+        for (int u = 0; u < 8; ++u) {
+          const int iu = i + u * groups;
+          r[u] = raw_zero<VB>();
+          sc[u] = 1;
+          if (iu < m && vact) {
+            r[u] = ld_stream_hint<VB>(static_cast<const char*>(a.grad) + entry_off[iu] + static_cast<int64_t>(v) * VB,
+                                      keep);
+            if (SCALED) sc[u] = entry_scale[iu];
+          }
         }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) add_grad<T, VB, SCALED>(r[u], sc[u], acc);
       }
-    };
+    }
+    __syncthreads();  // previous use of `part` finished
+#pragma unroll
+    for (int k = 0; k < NE; ++k) part[threadIdx.x * NE + k] = acc[k];
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < NE; ++k) total[k] = 0;
+    if (threadIdx.x < 32) {
+      for (int g = 0; g < groups; ++g) {
+#pragma unroll
+        for (int k = 0; k < NE; ++k) total[k] += part[(g * lpr + sub) * NE + k];
+      }
+    }
+  };
 
+  // Applies the optimizer to `row` given a way to obtain the summed gradient of chunk c of the run
+  // (every thread of warp 0 receives the total of its own `sub`); all threads of the CTA call it.
+  auto apply_run = [&](uint32_t row, auto&& chunk_total) {
+    char* wrow = static_cast<char*>(a.weights) + static_cast<int64_t>(row) * row_bytes;
     acc_t g2 = 0;
     if (OPT == kExactAdagrad && a.nchunks > 1) {
       for (int c = 0; c < a.nchunks; ++c) {
         acc_t tot[NE];
-        reduce_chunk(c, tot);
+        chunk_total(c, tot);
         const int v = (c << 5) + sub;
         if (v < a.nvec) g2 += sq_sum(tot, NE);
       }
@@ -889,7 +918,7 @@ __global__ void __launch_bounds__(kBwdThreads) long_run_kernel(const BwdArgs a) 
       const int v = (c << 5) + sub;
       const bool vact = v < a.nvec;
       acc_t tot[NE];
-      reduce_chunk(c, tot);
+      chunk_total(c, tot);
       if (APPROX) {  // the step sizes are inside the sum; `carry` holds the state after the whole run
         mult = 1;
         if (c == 0 && threadIdx.x == 0) a.state[row] = carry;
@@ -908,6 +937,52 @@ __global__ void __launch_bounds__(kBwdThreads) long_run_kernel(const BwdArgs a) 
         }
       }
     }
+  };
+
+  const bool splitting = a.split_len > 0;
+  for (int li = blockIdx.x; li < nlong; li += gridDim.x) {
+    const int2 run = a.long_list[li];
+    const int s = run.x, len = run.y - run.x;
+    if (splitting && len >= 2 * a.split_len) continue;  // cut into parts: see below
+    const uint32_t row = key_to_row(a.table_offsets, a.idx_bits, __ldg(a.keys + s));
+    const float st_first = APPROX ? a.state[row] : 0.f;  // read by every thread before thread 0 overwrites it
+    apply_run(row, [&](int c, acc_t* total) { reduce_range(c, s, len, st_first, total); });
+  }
+  if (!splitting) return;
+
+  // parts of split runs
+  const int nparts_total = min(*a.part_count, a.max_parts);
+  for (int p = blockIdx.x; p < nparts_total; p += gridDim.x) {
+    const int4 pm = a.part_list[p];  // {first entry, end entry, list index of the run's first part, parts of the run}
+    float* mine = a.part_sums + static_cast<int64_t>(p) * a.D;
+    for (int c = 0; c < a.nchunks; ++c) {
+      acc_t tot[NE];
+      reduce_range(c, pm.x, pm.y - pm.x, 0.f, tot);
+      const int v = (c << 5) + sub;
+      if (gid == 0 && v < a.nvec) {
+#pragma unroll
+        for (int k = 0; k < NE; ++k) mine[v * NE + k] = static_cast<float>(tot[k]);
+      }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) ticket = atomicAdd(a.part_tickets + pm.z, 1);
+    __syncthreads();
+    if (ticket != pm.w - 1) continue;  // another CTA will find all parts done
+    __threadfence();
+    const uint32_t row = key_to_row(a.table_offsets, a.idx_bits, __ldg(a.keys + pm.x));
+    apply_run(row, [&](int c, acc_t* total) {
+      const int v = (c << 5) + sub;
+#pragma unroll
+      for (int k = 0; k < NE; ++k) total[k] = 0;
+      if (threadIdx.x < 32 && v < a.nvec) {
+        for (int part_i = 0; part_i < pm.w; ++part_i) {  // part order: fixed
+          const float* ps = a.part_sums + static_cast<int64_t>(pm.z + part_i) * a.D + v * NE;
+#pragma unroll
+          for (int k = 0; k < NE; ++k) total[k] += static_cast<acc_t>(__ldcg(ps + k));
+        }
+      }
+    });
   }
 }
 
@@ -1111,6 +1186,26 @@ int exact_backward(int opt, const void* grad, int64_t stride_b, int64_t stride_t
   a.sr_offset = sr_offset;
   const bool mean = pooling == TBE_POOL_MEAN;
   const bool use_sr = sr != 0 && dtype == TBE_F16;
+  // Long runs are cut into parts when the part map and the fp32 partial sums fit the stretch of the
+  // workspace that the run-start list and the per-position arrays of other entry points occupy
+  // (3 N words, unused here).  The part length doubles until they fit.
+  a.split_len = 0;
+  if (opt != kApproxAdagrad && dtype != TBE_F64 && tuning(kTuneSplitRuns) != 1) {
+    const size_t region = static_cast<size_t>(reinterpret_cast<char*>(ws.hist) - reinterpret_cast<char*>(ws.seg_starts));
+    for (int64_t part = kMinSplitPart; part <= (1 << 16); part *= 2) {
+      const size_t max_parts = static_cast<size_t>(N / part + 1);
+      const size_t list_bytes = align_up(max_parts * sizeof(int4), 256), ticket_bytes = align_up(max_parts * sizeof(int32_t), 256);
+      if (list_bytes + ticket_bytes + max_parts * static_cast<size_t>(D) * sizeof(float) > region) continue;
+      char* base = reinterpret_cast<char*>(ws.seg_starts);
+      a.part_list = reinterpret_cast<int4*>(base);
+      a.part_tickets = reinterpret_cast<int32_t*>(base + list_bytes);
+      a.part_sums = reinterpret_cast<float*>(base + list_bytes + ticket_bytes);
+      a.part_count = ws.counters + 3;  // cleared with the other counters above
+      a.split_len = static_cast<int32_t>(part);
+      a.max_parts = static_cast<int32_t>(max_parts);
+      break;
+    }
+  }
   if (opt == kSGD) return dispatch_bwd<kSGD>(a, dtype, g.vb, mean, use_sr, stream);
   if (opt == kExactAdagrad) return dispatch_bwd<kExactAdagrad>(a, dtype, g.vb, mean, use_sr, stream);
   // approximate Adagrad: the bags' squared gradient norms go where the run-start list and the

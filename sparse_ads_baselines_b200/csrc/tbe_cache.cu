@@ -353,6 +353,13 @@ struct CachedSgdArgs {
   const int32_t* offsets;
   int2* long_list;      // runs longer than kLongCachedRun, handled by a whole CTA each
   int32_t* long_count;
+  // long runs cut into parts (0 = off): a part is split_len entries, the last one up to twice that
+  int32_t split_len, max_parts;
+  int4* part_list;       // {first entry, end entry, list index of the run's first part, parts of the run}
+  int32_t* part_run;     // at the list index of a run's first part: the run
+  int32_t* part_count;
+  int32_t* part_tickets; // at the list index of a run's first part: parts finished so far
+  float* part_sums;      // [max_parts][D]
   int32_t B, D, N, nvec, mean;
   int32_t lpr_log2;     // lanes per row in the long-run kernel
   float lr;
@@ -386,8 +393,21 @@ __global__ void __launch_bounds__(256) cached_sgd_kernel(const CachedSgdArgs a) 
        run += wstride) {
     const int s = __ldg(a.seg_starts + run);
     const int e = (run + 1 < U) ? __ldg(a.seg_starts + run + 1) : a.N;
-    if (e - s > kLongCachedRun) {  // a hot row: queued for the CTA-per-run kernel
-      if (lane == 0) a.long_list[atomicAdd(a.long_count, 1)] = make_int2(static_cast<int>(run), 0);
+    if (e - s > kLongCachedRun) {  // a hot row: queued for the CTA-per-run kernel, cut into parts if very long
+      if (lane == 0) {
+        a.long_list[atomicAdd(a.long_count, 1)] = make_int2(static_cast<int>(run), 0);
+        const int plen = a.split_len;
+        if (plen > 0 && e - s >= 2 * plen) {
+          const int nparts = (e - s) / plen;
+          const int base = atomicAdd(a.part_count, nparts);  // at most N / split_len parts exist in total
+          a.part_tickets[base] = 0;
+          a.part_run[base] = static_cast<int>(run);
+          for (int k = 0; k < nparts; ++k) {
+            const int ps = s + k * plen;
+            a.part_list[base + k] = make_int4(ps, k == nparts - 1 ? e : ps + plen, base, nparts);
+          }
+        }
+      }
       continue;
     }
     const int where = __ldg(a.loc_sorted + s);
@@ -426,14 +446,24 @@ __global__ void __launch_bounds__(256) cached_sgd_kernel(const CachedSgdArgs a) 
   }
 }
 
-// One CTA per queued long run: lane groups of lpr lanes take every G-th lookup of the run, four in
-// flight each; the groups' partial sums are folded in group order in shared memory, so the result
-// does not depend on scheduling.
+// Queued long runs.  A run is taken 256 entries at a time: every thread first turns one sorted entry
+// into the address of its gradient row (and 1/L for mean pooling) and leaves it in shared memory, so
+// that the row loads that follow depend on nothing but shared memory; lane groups of lpr lanes then
+// sum entries g, g + G, ... with eight loads in flight each, and the groups' partial sums are folded
+// in group order in shared memory.  A run shorter than two parts gets one CTA.  A longer one (the
+// hottest row of a Zipf table takes a sixth of the table's lookups) was cut into parts when it was
+// queued: any CTA sums a part into an fp32 partial, and the CTA that finishes a run's last outstanding
+// part (a ticket per run) adds the partials in part order and updates the row.  Every order of
+// summation is fixed by the sorted order and the part boundaries, never by scheduling.
 template <typename T, int VB>
 __global__ void __launch_bounds__(256) cached_sgd_long_kernel(const CachedSgdArgs a) {
   using acc_t = typename Acc<T>::type;
   constexpr int NE = VB / sizeof(T);
+  constexpr int kInFlight = 8;
   __shared__ acc_t part[256 * NE];
+  __shared__ int64_t entry_off[256];
+  __shared__ acc_t entry_scale[256];
+  __shared__ int ticket;
   const int lpr = 1 << a.lpr_log2;
   const int sub = threadIdx.x & (lpr - 1);
   const int gid = threadIdx.x >> a.lpr_log2;
@@ -441,52 +471,73 @@ __global__ void __launch_bounds__(256) cached_sgd_long_kernel(const CachedSgdArg
   const int U = __ldg(a.counters);
   const int nlong = *a.long_count;
   const int64_t row_bytes = static_cast<int64_t>(a.D) * sizeof(T);
-  for (int li = blockIdx.x; li < nlong; li += gridDim.x) {
-    const int run = a.long_list[li].x;
-    const int s = __ldg(a.seg_starts + run);
-    const int e = (run + 1 < U) ? __ldg(a.seg_starts + run + 1) : a.N;
-    const int where = __ldg(a.loc_sorted + s);
-    char* w = where >= 0 ? static_cast<char*>(a.cache_rows) + static_cast<int64_t>(where) * row_bytes
-                         : static_cast<char*>(a.host_rows) + static_cast<int64_t>(__ldg(a.run_row + run)) * row_bytes;
-    if (threadIdx.x == 0 && where >= 0) a.dirty[where] = 1;
-    for (int c = 0; c * lpr < a.nvec; ++c) {
-      const int v = c * lpr + sub;
-      const bool vact = v < a.nvec;
-      acc_t acc[NE];
+
+  // sum of chunk c of the gradient rows of sorted entries [s, e); the threads of group 0 receive it
+  auto sum_range = [&](int c, int s, int e, acc_t* tot) {
+    const int v = c * lpr + sub;
+    const bool vact = v < a.nvec;
+    acc_t acc[NE];
 #pragma unroll
-      for (int k = 0; k < NE; ++k) acc[k] = 0;
-      for (int i = s + gid; i < e; i += 4 * G) {
-        int bag[4];
-        Raw<VB> r[4];
-        acc_t sc[4];
+    for (int k = 0; k < NE; ++k) acc[k] = 0;
+    for (int base = s; base < e; base += 256) {
+      const int m = min(256, e - base);
+      __syncthreads();  // the previous block of entries has been consumed
+      if (static_cast<int>(threadIdx.x) < m) {
+        const int bag = __ldg(a.entry_bag + __ldg(a.vals + base + threadIdx.x));
+        const int t = bag / a.B;
+        const int b = bag - t * a.B;
+        entry_off[threadIdx.x] = (static_cast<int64_t>(b) * a.stride_b + static_cast<int64_t>(t) * a.stride_t) *
+                                 static_cast<int64_t>(sizeof(T));
+        entry_scale[threadIdx.x] =
+            a.mean ? acc_t(1) / static_cast<acc_t>(__ldg(a.offsets + bag + 1) - __ldg(a.offsets + bag)) : acc_t(1);
+      }
+      __syncthreads();
+      for (int i = gid; i < m; i += G * kInFlight) {
+        Raw<VB> r[kInFlight];
+        acc_t sc[kInFlight];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) bag[u] = (i + u * G < e) ? __ldg(a.entry_bag + __ldg(a.vals + i + u * G)) : -1;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < kInFlight; ++u) {
+          const int iu = i + u * G;
           r[u] = raw_zero<VB>();
           sc[u] = 1;
-          if (bag[u] >= 0 && vact) r[u] = cached_grad<T, VB>(a, bag[u], v, &sc[u]);
+          if (iu < m && vact) {
+            r[u] = ld_stream<VB>(static_cast<const char*>(a.grad) + entry_off[iu] + static_cast<int64_t>(v) * VB);
+            sc[u] = entry_scale[iu];
+          }
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < kInFlight; ++u) {
           acc_t g[NE];
           unpack<T, VB>(r[u], g);
 #pragma unroll
           for (int k = 0; k < NE; ++k) acc[k] += g[k] * sc[u];
         }
       }
-      __syncthreads();  // the previous chunk's partial sums have been consumed
+    }
+    __syncthreads();  // the previous use of `part` has been consumed
 #pragma unroll
-      for (int k = 0; k < NE; ++k) part[threadIdx.x * NE + k] = acc[k];
-      __syncthreads();
-      if (gid == 0 && vact) {
-        acc_t tot[NE];
+    for (int k = 0; k < NE; ++k) part[threadIdx.x * NE + k] = acc[k];
+    __syncthreads();
 #pragma unroll
-        for (int k = 0; k < NE; ++k) tot[k] = 0;
-        for (int g = 0; g < G; ++g) {
+    for (int k = 0; k < NE; ++k) tot[k] = 0;
+    if (gid == 0 && vact) {
+      for (int g = 0; g < G; ++g) {
 #pragma unroll
-          for (int k = 0; k < NE; ++k) tot[k] += part[(g * lpr + sub) * NE + k];
-        }
+        for (int k = 0; k < NE; ++k) tot[k] += part[(g * lpr + sub) * NE + k];
+      }
+    }
+  };
+  // row -= lr * total, chunk by chunk; the row lives in the cache (marked dirty) or in the host table
+  auto update_row = [&](int run, int s, auto&& chunk_total) {
+    const int where = __ldg(a.loc_sorted + s);
+    char* w = where >= 0 ? static_cast<char*>(a.cache_rows) + static_cast<int64_t>(where) * row_bytes
+                         : static_cast<char*>(a.host_rows) + static_cast<int64_t>(__ldg(a.run_row + run)) * row_bytes;
+    if (threadIdx.x == 0 && where >= 0) a.dirty[where] = 1;
+    for (int c = 0; c * lpr < a.nvec; ++c) {
+      const int v = c * lpr + sub;
+      acc_t tot[NE];
+      chunk_total(c, tot);
+      if (gid == 0 && v < a.nvec) {
         acc_t x[NE];
         unpack<T, VB>(ld_rw<VB>(w + static_cast<int64_t>(v) * VB), x);
 #pragma unroll
@@ -494,6 +545,49 @@ __global__ void __launch_bounds__(256) cached_sgd_long_kernel(const CachedSgdArg
         st_row<VB>(w + static_cast<int64_t>(v) * VB, pack_rn<T, VB>(x));
       }
     }
+  };
+
+  for (int li = blockIdx.x; li < nlong; li += gridDim.x) {
+    const int run = a.long_list[li].x;
+    const int s = __ldg(a.seg_starts + run);
+    const int e = (run + 1 < U) ? __ldg(a.seg_starts + run + 1) : a.N;
+    if (a.split_len > 0 && e - s >= 2 * a.split_len) continue;  // cut into parts: below
+    update_row(run, s, [&](int c, acc_t* tot) { sum_range(c, s, e, tot); });
+  }
+  if (a.split_len <= 0) return;
+  const int nparts_total = min(*a.part_count, a.max_parts);
+  for (int p = blockIdx.x; p < nparts_total; p += gridDim.x) {
+    const int4 pm = a.part_list[p];  // {first entry, end entry, list index of the run's first part, parts of the run}
+    float* mine = a.part_sums + static_cast<int64_t>(p) * a.D;
+    for (int c = 0; c * lpr < a.nvec; ++c) {
+      acc_t tot[NE];
+      sum_range(c, pm.x, pm.y, tot);
+      const int v = c * lpr + sub;
+      if (gid == 0 && v < a.nvec) {
+#pragma unroll
+        for (int k = 0; k < NE; ++k) mine[v * NE + k] = static_cast<float>(tot[k]);
+      }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) ticket = atomicAdd(a.part_tickets + pm.z, 1);
+    __syncthreads();
+    if (ticket != pm.w - 1) continue;  // another CTA will find all parts done
+    __threadfence();
+    const int4 first = a.part_list[pm.z];
+    const int run = a.part_run[pm.z];
+    update_row(run, first.x, [&](int c, acc_t* tot) {
+      const int v = c * lpr + sub;
+#pragma unroll
+      for (int k = 0; k < NE; ++k) tot[k] = 0;
+      if (gid == 0 && v < a.nvec) {
+        for (int part_i = 0; part_i < pm.w; ++part_i) {  // part order: fixed
+          const float* ps = a.part_sums + static_cast<int64_t>(pm.z + part_i) * a.D + v * NE;
+#pragma unroll
+          for (int k = 0; k < NE; ++k) tot[k] += static_cast<acc_t>(__ldcg(ps + k));
+        }
+      }
+    });
   }
 }
 
@@ -784,6 +878,28 @@ extern "C" int tbe_cache_backward_sgd(const void* grad_output, int64_t stride_b,
   a.lr = lr;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   TBE_CUDA_TRY(cudaMemsetAsync(cs.ws.counters + 1, 0, 4, stream));  // the long-run queue starts empty
+  // very long runs are cut into parts; the part list, the tickets and the fp32 partial sums live where
+  // the sort's input pairs were (dead since the prefetch sorted them)
+  a.split_len = 0;
+  {
+    const size_t region =
+        static_cast<size_t>(reinterpret_cast<char*>(cs.ws.seg_starts) - reinterpret_cast<char*>(cs.ws.keys_in));
+    for (int64_t plen = 256; plen <= (1 << 16); plen *= 2) {
+      const size_t max_parts = static_cast<size_t>(N / plen + 1);
+      const size_t list_bytes = align_up(max_parts * sizeof(int4), 256), word_bytes = align_up(max_parts * sizeof(int32_t), 256);
+      if (list_bytes + 2 * word_bytes + max_parts * static_cast<size_t>(D) * sizeof(float) > region) continue;
+      char* base = reinterpret_cast<char*>(cs.ws.keys_in);
+      a.part_list = reinterpret_cast<int4*>(base);
+      a.part_tickets = reinterpret_cast<int32_t*>(base + list_bytes);
+      a.part_run = reinterpret_cast<int32_t*>(base + list_bytes + word_bytes);
+      a.part_sums = reinterpret_cast<float*>(base + list_bytes + 2 * word_bytes);
+      a.part_count = cs.ws.counters + 9;
+      a.split_len = static_cast<int32_t>(plen);
+      a.max_parts = static_cast<int32_t>(max_parts);
+      TBE_CUDA_TRY(cudaMemsetAsync(a.part_count, 0, 4, stream));
+      break;
+    }
+  }
   {
     KernelTimer timer("cached_sgd_kernel", stream);
     const int grid = grid_for(N);
@@ -795,7 +911,7 @@ extern "C" int tbe_cache_backward_sgd(const void* grad_output, int64_t stride_b,
   TBE_CHECK_LAUNCH("cached_sgd_kernel");
   {
     KernelTimer timer("cached_sgd_long_kernel", stream);
-    const int grid = device_sm_count() * 2;
+    const int grid = device_sm_count() * 6;
     if (dtype == TBE_F16 && vb == 16) cached_sgd_long_kernel<__half, 16><<<grid, 256, 0, stream>>>(a);
     else if (dtype == TBE_F16) cached_sgd_long_kernel<__half, 8><<<grid, 256, 0, stream>>>(a);
     else cached_sgd_long_kernel<float, 16><<<grid, 256, 0, stream>>>(a);

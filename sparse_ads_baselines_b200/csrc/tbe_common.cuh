@@ -34,6 +34,7 @@ enum Tuning {
   kTuneBwdVpl,
   kTuneBwdSort,     // 0: two-level bucket sort when the batch suits it, 1: always the device radix sort
   kTuneSortBucket,  // wanted mean bucket size of the two-level sort (0: default)
+  kTuneSplitRuns,   // 1: never cut long runs into parts (one CTA per queued run)
   kTuneCount
 };
 

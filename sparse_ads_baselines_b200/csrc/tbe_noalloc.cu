@@ -5,7 +5,8 @@
 // a serving process whose HBM is budgeted completely at start-up forbids a cudaMalloc in the request
 // path (besides failing when the budget is spent, cudaMalloc synchronises the whole device).  For
 // them the sort scratch of tbe_backward_sgd lives inside the library, in a fixed array in device
-// memory that every GPU using the library holds from load to exit.
+// memory.  CUDA materialises a library's device image lazily, so a GPU starts holding the array at
+// the first call made on it (a warm-up call at start-up reserves it) and keeps it until exit.
 //
 // The array is shared by all calls on a device and keeps whatever the previous call left in it:
 // each call re-initialises the few words that must start at zero (the long-run counters) before it

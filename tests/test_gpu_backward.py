@@ -204,6 +204,46 @@ def test_long_segments(cuda_device, opt, dtype):
         assert_close(w1, ref, dtype)
 
 
+@pytest.mark.parametrize("opt", ["sgd", "adagrad"])
+@pytest.mark.parametrize("dtype,D,pooling", [(torch.float32, 128, "mean"), (torch.float16, 128, "sum"), (torch.float32, 260, "sum")])
+def test_hot_rows_are_split_over_several_ctas(cuda_device, opt, dtype, D, pooling):
+    """Rows with thousands of lookups: the queued run is cut into parts that different CTAs sum, and
+    the CTA finishing the last part folds them in part order.  Results must match the oracle, be
+    bit-identical from call to call, and agree with the one-CTA-per-run path (knob split_runs = 1)."""
+    T, E, B, L = 2, 3, 3000, 2   # ~2,000 lookups per row: 7 parts of 256 entries
+    c = to_device(make_case(T=T, E=E, D=D, B=B, Lmax=L, dtype=dtype, seed=31, fixed_L=L), cuda_device)
+    c["grad_d"] = (c["grad_d"] * 0.01).contiguous()
+    c["grad"] = c["grad_d"].cpu()
+    s0 = torch.rand(T * E, device=cuda_device) * 0.1
+
+    def run():
+        if opt == "sgd":
+            w = c["weights_d"].clone()
+            tbe.backward_sgd(c["grad_d"], w, c["table_offsets_d"], c["indices_d"], c["offsets_d"], 0.05, 200, 1, False,
+                             pooling_mode=pooling)
+            return w, None
+        return _adagrad(c, s0, 0.5, 0.2, pooling=pooling)
+
+    w1, s1 = run()
+    w2, s2 = run()
+    assert torch.equal(w1, w2) and (s1 is None or torch.equal(s1, s2))
+    try:
+        _lib.call("tbe_set_tuning", b"split_runs", 1)
+        w3, s3 = run()
+    finally:
+        _lib.call("tbe_set_tuning", b"split_runs", 0)
+    tol = dict(rtol=1e-2, atol=1e-2) if dtype == torch.float16 else dict(rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(w1.float(), w3.float(), **tol)
+    if opt == "sgd":
+        ref = oracle.sgd_step(c["weights"], c["table_offsets"], c["indices"], c["offsets"], c["grad"], 0.05, pooling,
+                              compute_dtype=torch.float32)
+    else:
+        ref, rs = oracle.exact_rowwise_adagrad_step(c["weights"], s0.cpu(), c["table_offsets"], c["indices"],
+                                                    c["offsets"], c["grad"], 0.5, 0.2, pooling)
+        torch.testing.assert_close(s1.cpu(), rs, rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(w1.float().cpu(), ref.float(), **tol)
+
+
 def test_backward_is_deterministic(cuda_device):
     c = to_device(make_case(T=4, E=30, D=128, B=256, Lmax=10, dtype=torch.float16, seed=9), cuda_device)
     a = _sgd(c, 0.1)

@@ -117,11 +117,13 @@ def test_hit_rate_grows_with_reuse(cuda_device):
     assert rates[0] == 0.0 and rates[-1] > 0.5, rates
 
 
+@pytest.mark.parametrize("B", [300, 4000])
 @pytest.mark.parametrize("fp16,D", [(False, 32), (True, 128), (False, 260)])
-def test_hot_rows_take_the_long_run_path(cuda_device, fp16, D):
+def test_hot_rows_take_the_long_run_path(cuda_device, fp16, D, B):
     """A few rows receive hundreds of lookups each (more than the 64 a single warp handles): the
-    CTA-per-run kernel must give the oracle's SGD update, deterministically."""
-    T, E, B, L, lr = 2, 6, 300, 3, 0.01
+    CTA-per-run kernel must give the oracle's SGD update, deterministically.  With B = 4000 a row
+    sees ~2,000 lookups and its run is cut into parts summed by several CTAs."""
+    T, E, L, lr = 2, 6, 3, 0.01
     dtype = torch.float16 if fp16 else torch.float32
     cached = LXUCachedEmbeddingBags(T, E, D, cache_rows=8, ways=4, policy="lru", learning_rate=lr, fp16=fp16)
     torch.manual_seed(1)
