@@ -387,7 +387,11 @@ def measure(args, w, rank, world, local_rank, rotate=ROTATE, with_e2e=True, with
     # `rotate` distinct batches; every rank draws the global batch for its own tables
     batches = make_batches(w, rank, device, rotate)
     gen = torch.Generator(device=device).manual_seed(99 + rank)
-    grad = torch.randn(Bl, w.T * world, w.D, device=device, generator=gen).to(tdt)  # upstream gradient, local slice
+    grad = torch.empty(Bl, w.T * world, w.D, device=device, dtype=tdt)  # upstream gradient, local slice
+    rows_per_chunk = max(1, (1 << 28) // (w.T * world * w.D))      # filled in chunks: no full-size fp32 temporary
+    for b0 in range(0, Bl, rows_per_chunk):
+        grad[b0:b0 + rows_per_chunk] = torch.randn(min(rows_per_chunk, Bl - b0), w.T * world, w.D, device=device,
+                                                   generator=gen).to(tdt)
     N = sum(b["N"] for b in batches) / rotate   # mean lookups per step (ragged workloads differ per batch)
     nbags = w.T * w.B
 
@@ -522,12 +526,14 @@ def measure(args, w, rank, world, local_rank, rotate=ROTATE, with_e2e=True, with
     return line
 
 
-def cfg5_workload(world):
+def cfg5_workload(world, tables=0):
     """Config 5 at ``world`` ranks: 512 tables re-sharded 512/world per rank, global batch 65,536
     (pytorch_distributed_benchmark.py:208-231).  One rank cannot hold all 512 tables plus the batch,
     so ``world`` = 1 runs one rank's share of the 8-rank problem (64 tables)."""
     import dataclasses
     base = workloads.WORKLOADS["cfg5"]
+    if tables > 0:
+        return dataclasses.replace(base, T=tables)
     return dataclasses.replace(base, T=(512 // world) if world > 1 else 64)
 
 
@@ -540,7 +546,8 @@ def run_ours(args, rank, world, local_rank):
         knob, val = pair.split("=")
         _lib.call("tbe_set_tuning", knob.encode(), int(val))
     if args.workload == "cfg5":
-        line = measure(args, cfg5_workload(world), rank, world, local_rank, rotate=2, with_e2e=False, regions=3)
+        line = measure(args, cfg5_workload(world, args.cfg5_tables), rank, world, local_rank,
+                       rotate=1 if args.cfg5_tables > 256 else 2, with_e2e=False, regions=3)
     else:
         line = measure(args, workloads.WORKLOADS[args.workload], rank, world, local_rank)
         if world > 1 and args.workload == "target" and not args.no_cfg5:
@@ -790,6 +797,9 @@ def main():
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
+    ap.add_argument("--cfg5-tables", type=int, default=0,
+                    help="--workload cfg5: tables per rank (default 512/N, or 64 on one GPU; 512 = the whole of "
+                         "config 5 on one GPU, which needs nearly all of its memory)")
     ap.add_argument("--no-cfg5", action="store_true",
                     help="multi-GPU runs of the target also time config 5 at its own shapes; this skips it")
     ap.add_argument("--plan-ahead", type=int, default=0,

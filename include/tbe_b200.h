@@ -369,7 +369,18 @@ TBE_API int tbe_cache_prefetch(void* cache_rows, int32_t* tags, int32_t* last_us
                                const int32_t* indices, const int32_t* offsets, int32_t* locations,
                                int32_t* stats, int64_t T, int64_t B, int64_t D, int64_t N,
                                int64_t total_rows, int64_t num_sets, int ways, int dtype, int policy,
-                               int now, void* workspace, int64_t workspace_bytes, void* stream);
+                               int now, void* writeback_rows, int32_t* writeback_ids,
+                               void* workspace, int64_t workspace_bytes, void* stream);
+/* Deferred write-backs.  With writeback_rows / writeback_ids (both or neither; device buffers of
+ * min(N, num_sets*ways) rows of the table dtype and as many int32) tbe_cache_prefetch does not write
+ * dirty victims to host_rows: it stages them there, and tbe_cache_writeback -- on any stream ordered
+ * after the prefetch, e.g. a side stream running under the lookup -- carries them to host_rows.  Only
+ * the fetches then sit on the critical path of the host link.  The caller orders the next
+ * tbe_cache_prefetch, tbe_cache_flush and any host read of the table after the write-back (an
+ * evicted row is never looked up in the step that evicted it, so the lookup itself needs no order).
+ * `stats` is the array the prefetch wrote (its second word is the number of staged slots). */
+TBE_API int tbe_cache_writeback(const void* writeback_rows, const int32_t* writeback_ids, const int32_t* stats,
+                                void* host_rows, int64_t D, int dtype, void* stream);
 /* Pooled forward reading every row through `locations` (sum / mean, fp16 / fp32). */
 TBE_API int tbe_cache_forward(const void* cache_rows, const void* host_rows,
                               const int32_t* table_offsets, const int32_t* indices,

@@ -86,7 +86,7 @@ int device_sm_count() {
 }
 }  // namespace tbe
 
-extern "C" int tbe_abi_version(void) { return 3; }
+extern "C" int tbe_abi_version(void) { return 4; }
 
 extern "C" const char* tbe_last_error_string(void) { return tbe::g_error; }
 

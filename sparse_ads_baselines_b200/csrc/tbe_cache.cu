@@ -201,8 +201,15 @@ __global__ void __launch_bounds__(256) cache_update_kernel(const CacheArgs a) {
 // alias: a row fetched in this step was not cached, a row evicted in this step was not looked up.
 constexpr int kFillBatch = 4;
 
+//
+// Write-backs can be deferred: with a staging buffer (wb_rows, one row per claim, in HBM) the dirty
+// victim is copied there instead of to the host table, wb_ids[claim] records where it belongs (-1:
+// nothing to write back), and cache_writeback_kernel carries the staged rows to the host later -- on
+// another stream, under the lookup that follows -- so that only the fetches stay on the critical path
+// of the host link.
 template <int VB>
-__global__ void __launch_bounds__(256) cache_fill_kernel(const CacheArgs a, int64_t row_bytes, int lpr_log2) {
+__global__ void __launch_bounds__(256) cache_fill_kernel(const CacheArgs a, int64_t row_bytes, int lpr_log2,
+                                                         char* __restrict__ wb_rows, int32_t* __restrict__ wb_ids) {
   const int lpr = 1 << lpr_log2;
   const int sub = threadIdx.x & (lpr - 1);
   const int64_t group = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> lpr_log2;
@@ -232,14 +239,52 @@ __global__ void __launch_bounds__(256) cache_fill_kernel(const CacheArgs a, int6
 #pragma unroll
       for (int u = 0; u < kFillBatch; ++u) {
         char* crow = static_cast<char*>(a.cache_rows) + static_cast<int64_t>(cl[u].x) * row_bytes;
-        char* hrow = static_cast<char*>(a.host_rows) + static_cast<int64_t>(cl[u].y) * row_bytes;
-        if (back[u]) st_row<VB>(hrow + static_cast<int64_t>(v) * VB, old_row[u]);
+        char* back_to = wb_rows != nullptr
+                            ? wb_rows + (c0 + static_cast<int64_t>(u) * ngroups) * row_bytes
+                            : static_cast<char*>(a.host_rows) + static_cast<int64_t>(cl[u].y) * row_bytes;
+        if (back[u]) st_row<VB>(back_to + static_cast<int64_t>(v) * VB, old_row[u]);
         if (live[u]) st_row<VB>(crow + static_cast<int64_t>(v) * VB, new_row[u]);
       }
     }
 #pragma unroll
-    for (int u = 0; u < kFillBatch; ++u)
-      if (live[u] && sub == 0) a.dirty[cl[u].x] = 0;
+    for (int u = 0; u < kFillBatch; ++u) {
+      if (live[u] && sub == 0) {
+        a.dirty[cl[u].x] = 0;
+        if (wb_ids != nullptr) wb_ids[c0 + static_cast<int64_t>(u) * ngroups] = back[u] ? cl[u].y : -1;
+      }
+    }
+  }
+}
+
+// Staged victim rows -> host table.  A small grid is enough: the host link, not the SMs, is the limit.
+template <int VB>
+__global__ void __launch_bounds__(256) cache_writeback_kernel(const char* __restrict__ wb_rows,
+                                                              const int32_t* __restrict__ wb_ids,
+                                                              const int32_t* __restrict__ nclaims_ptr, char* host_rows,
+                                                              int64_t row_bytes, int nvec, int lpr_log2) {
+  const int lpr = 1 << lpr_log2;
+  const int sub = threadIdx.x & (lpr - 1);
+  const int64_t group = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> lpr_log2;
+  const int64_t ngroups = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> lpr_log2;
+  const int nclaims = *nclaims_ptr;
+  for (int64_t c0 = group; c0 < nclaims; c0 += ngroups * kFillBatch) {
+    int32_t id[kFillBatch];
+#pragma unroll
+    for (int u = 0; u < kFillBatch; ++u) {
+      const int64_t c = c0 + u * ngroups;
+      id[u] = c < nclaims ? __ldg(wb_ids + c) : -1;
+    }
+    for (int v = sub; v < nvec; v += lpr) {
+      Raw<VB> r[kFillBatch];
+#pragma unroll
+      for (int u = 0; u < kFillBatch; ++u) {
+        r[u] = raw_zero<VB>();
+        if (id[u] >= 0) r[u] = ld_stream<VB>(wb_rows + (c0 + static_cast<int64_t>(u) * ngroups) * row_bytes + static_cast<int64_t>(v) * VB);
+      }
+#pragma unroll
+      for (int u = 0; u < kFillBatch; ++u)
+        if (id[u] >= 0) st_row<VB>(host_rows + static_cast<int64_t>(id[u]) * row_bytes + static_cast<int64_t>(v) * VB, r[u]);
+    }
   }
 }
 
@@ -674,10 +719,13 @@ extern "C" int tbe_cache_prefetch(void* cache_rows, int32_t* tags, int32_t* last
                                   uint8_t* dirty, void* host_rows, const int32_t* table_offsets,
                                   const int32_t* indices, const int32_t* offsets, int32_t* locations,
                                   int32_t* stats, int64_t T, int64_t B, int64_t D, int64_t N, int64_t total_rows,
-                                  int64_t num_sets, int ways, int dtype, int policy, int now, void* workspace,
-                                  int64_t workspace_bytes, void* stream_v) {
+                                  int64_t num_sets, int ways, int dtype, int policy, int now, void* writeback_rows,
+                                  int32_t* writeback_ids, void* workspace, int64_t workspace_bytes,
+                                  void* stream_v) {
   using namespace tbe;
   const char* who = "tbe_cache_prefetch";
+  TBE_REQUIRE((writeback_rows == nullptr) == (writeback_ids == nullptr),
+              "%s: writeback_rows and writeback_ids go together", who);
   TBE_REQUIRE(cache_rows && tags && last_use && use_count && dirty && host_rows && table_offsets && offsets &&
                   locations && stats && (indices || N == 0),
               "%s: null pointer argument", who);
@@ -768,9 +816,11 @@ extern "C" int tbe_cache_prefetch(void* cache_rows, int32_t* tags, int32_t* last
   {
     KernelTimer timer("cache_fill_kernel", stream);
     if (vb == 16) {
-      cache_fill_kernel<16><<<grid_for(N), 256, 0, stream>>>(a, row_bytes, fill_lpr_log2);
+      cache_fill_kernel<16><<<grid_for(N), 256, 0, stream>>>(a, row_bytes, fill_lpr_log2,
+                                                             static_cast<char*>(writeback_rows), writeback_ids);
     } else {
-      cache_fill_kernel<8><<<grid_for(N), 256, 0, stream>>>(a, row_bytes, fill_lpr_log2);
+      cache_fill_kernel<8><<<grid_for(N), 256, 0, stream>>>(a, row_bytes, fill_lpr_log2,
+                                                            static_cast<char*>(writeback_rows), writeback_ids);
     }
   }
   TBE_CHECK_LAUNCH("cache_fill_kernel");
@@ -783,6 +833,36 @@ extern "C" int tbe_cache_prefetch(void* cache_rows, int32_t* tags, int32_t* last
   //         distinct rows already cached, distinct rows left uncached}
   TBE_CUDA_TRY(cudaMemcpyAsync(stats, cs.ws.counters, 4, cudaMemcpyDeviceToDevice, stream));
   TBE_CUDA_TRY(cudaMemcpyAsync(stats + 1, cs.ws.counters + 2, 16, cudaMemcpyDeviceToDevice, stream));
+  return TBE_OK;
+}
+
+extern "C" int tbe_cache_writeback(const void* writeback_rows, const int32_t* writeback_ids, const int32_t* stats,
+                                   void* host_rows, int64_t D, int dtype, void* stream_v) {
+  using namespace tbe;
+  const char* who = "tbe_cache_writeback";
+  TBE_REQUIRE(writeback_rows && writeback_ids && stats && host_rows, "%s: null pointer argument", who);
+  TBE_REQUIRE(D > 0 && D % 4 == 0, "%s: D must be a positive multiple of 4", who);
+  int vb = 16, nvec = 0;
+  int rc = vector_bytes(who, D, dtype, writeback_rows, host_rows, nullptr, &vb, &nvec);
+  if (rc != TBE_OK) return rc;
+  const int64_t row_bytes = D * elem_size(dtype);
+  int lpr_log2 = 0;
+  while ((1 << lpr_log2) < nvec && lpr_log2 < 5) ++lpr_log2;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const int grid = 64;  // link-bound: a few thousand threads keep it full without taking SMs from the lookup
+  {
+    KernelTimer timer("cache_writeback_kernel", stream);
+    if (vb == 16) {
+      cache_writeback_kernel<16><<<grid, 256, 0, stream>>>(static_cast<const char*>(writeback_rows), writeback_ids,
+                                                           stats + 1, static_cast<char*>(host_rows), row_bytes, nvec,
+                                                           lpr_log2);
+    } else {
+      cache_writeback_kernel<8><<<grid, 256, 0, stream>>>(static_cast<const char*>(writeback_rows), writeback_ids,
+                                                          stats + 1, static_cast<char*>(host_rows), row_bytes, nvec,
+                                                          lpr_log2);
+    }
+  }
+  TBE_CHECK_LAUNCH("cache_writeback_kernel");
   return TBE_OK;
 }
 

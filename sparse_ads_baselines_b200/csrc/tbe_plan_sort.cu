@@ -48,7 +48,8 @@ constexpr int kRankMaxGroup = kBucketSortMaxGroup;              // most pairs on
 static_assert(kBucketSortCapacity <= 2048 && kRankMaxGroup < 1024, "packing of bucket_rank_kernel's `where`");
 constexpr int kOversizeThreads = 1024;
 constexpr int kOversizeWarps = kOversizeThreads / 32;
-constexpr int kMaxDigits = 256;             // radix passes look at up to 8 bits
+constexpr int kMaxDigits = 128;             // radix passes look at up to 7 bits
+constexpr int kDigitBits = 7;
 constexpr int kFewBuckets = 1024;           // buckets per table the narrow kernel variants hold in shared memory
 constexpr int kMaxBuckets = 4096;           // buckets per table (wide variants: busy tables, e.g. 2 lookups per row)
 constexpr int kBucketIdBits = 12;           // log2(kMaxBuckets)
@@ -591,28 +592,134 @@ __device__ __forceinline__ void radix_pass(const uint32_t* sk, const int32_t* sv
   __syncthreads();
 }
 
-// Buckets too large for bucket_rank_kernel: least-significant-digit radix sort on (index bits, bag
-// id within the table).  The bucket's pairs are first split into the output arrays; the passes then
-// ping-pong between those and the bucket's own stretch of the pair array, which is free by then.  A
-// fixed grid walks the queue, so an empty queue costs one launch.
+// The same stable pass over n 32-bit words (shared memory to shared memory).  (Finding the lanes with
+// equal digits with one match instruction instead of `dbits` ballots was measured and is slower here.)
+template <int W>
+__device__ __forceinline__ void radix_pass_words(const uint32_t* src, uint32_t* dst, int32_t n, int sh, int dbits,
+                                                 int32_t* cnt, int32_t* digit_base) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int nd = 1 << dbits;
+  const uint32_t mask = static_cast<uint32_t>(nd - 1);
+  int32_t ca, cb;
+  warp_share(0, n, w, W, &ca, &cb);
+  int32_t* my_cnt = cnt + w * kMaxDigits;
+  for (int i = lane; i < nd; i += 32) my_cnt[i] = 0;
+  __syncwarp();
+  for (int32_t p = ca + lane; p < cb; p += 32) atomicAdd(&my_cnt[(src[p] >> sh) & mask], 1);
+  __syncthreads();
+  for (int d = threadIdx.x; d < nd; d += W * 32) {
+    int32_t run = 0;
+#pragma unroll 8
+    for (int w2 = 0; w2 < W; ++w2) {
+      const int32_t c = cnt[w2 * kMaxDigits + d];
+      cnt[w2 * kMaxDigits + d] = run;
+      run += c;
+    }
+    digit_base[d] = run;
+  }
+  __syncthreads();
+  if (w == 0) {  // exclusive scan of the per-digit totals
+    constexpr int kPer = kMaxDigits / 32;
+    int32_t v[kPer];
+    int32_t sum = 0;
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int d = lane * kPer + j;
+      v[j] = d < nd ? digit_base[d] : 0;
+      sum += v[j];
+    }
+    int32_t incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    int32_t run = incl - sum;
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int d = lane * kPer + j;
+      if (d < nd) digit_base[d] = run;
+      run += v[j];
+    }
+  }
+  __syncthreads();
+  for (int32_t p0 = ca; p0 < cb; p0 += 32) {
+    const int32_t p = p0 + lane;
+    const bool valid = p < cb;
+    const uint32_t x = valid ? src[p] : 0u;
+    const uint32_t d = (x >> sh) & mask;
+    uint32_t peers = __ballot_sync(0xffffffffu, valid);
+    for (int bit = 0; bit < dbits; ++bit) {
+      const bool one = (d >> bit) & 1u;
+      const uint32_t set = __ballot_sync(0xffffffffu, one);
+      peers &= one ? set : ~set;
+    }
+    const int r = __popc(peers & ((1u << lane) - 1u));
+    if (valid) dst[digit_base[d] + my_cnt[d] + r] = x;
+    __syncwarp();
+    if (valid && r == 0) my_cnt[d] += __popc(peers);
+    __syncwarp();
+  }
+  __syncthreads();
+}
+
+// Buckets too large for bucket_rank_kernel (or with a hot row): least-significant-digit radix sort on
+// (index bits, bag id within the table), one 1024-thread CTA per queued bucket.  A fixed grid walks
+// the queue, so an empty queue costs one launch.
+//
+// When the bucket fits (the usual case: the first bucket of a skewed table holds ~25,000 pairs) the
+// sort runs entirely in shared memory: a pair's index bits and its bag id within the table are packed
+// into one 32-bit word, index bits on top, so that ascending words ARE the order by (index, bag); two
+// word buffers of `smem_capacity` entries ping-pong through the passes and keys and bag ids are
+// rebuilt on the way out.  Larger buckets (or more than 32 bits) take the passes through global
+// memory: the bucket's pairs are first split into the output arrays, the passes then ping-pong
+// between those and the bucket's own stretch of the pair array, which is free by then.
 __global__ void __launch_bounds__(kOversizeThreads) oversize_sort_kernel(uint2* pairs, uint32_t* kout, int32_t* vout,
                                                                          int key_bits, int bag_bits, int idx_bits,
                                                                          int32_t B,
                                                                          const int32_t* __restrict__ queue_count,
                                                                          const int2* __restrict__ queue,
-                                                                         int queue_cap) {
+                                                                         int queue_cap, int smem_capacity) {
+  extern __shared__ uint32_t words[];  // 2 * smem_capacity
   __shared__ int32_t cnt[kOversizeWarps * kMaxDigits];
   __shared__ int32_t digit_base[kMaxDigits];
   const int count = min(*queue_count, queue_cap);
-  const int vp = (bag_bits + 7) / 8, kp = (key_bits + 7) / 8;
+  const int vp = (bag_bits + kDigitBits - 1) / kDigitBits, kp = (key_bits + kDigitBits - 1) / kDigitBits;
   const int vd = vp ? (bag_bits + vp - 1) / vp : 0, kd = kp ? (key_bits + kp - 1) / kp : 0;
   for (int q = blockIdx.x; q < count; q += gridDim.x) {
     const int2 seg = queue[q];
     const int32_t n = seg.y - seg.x;
+    const uint32_t first_key = pairs[seg.x].x;
+    const int32_t vbase = static_cast<int32_t>(first_key >> idx_bits) * B;  // first bag of the bucket's table
+    if (n <= smem_capacity && key_bits + bag_bits <= 32) {
+      const uint32_t low_mask = key_bits >= 32 ? 0xffffffffu : ((1u << key_bits) - 1u);
+      const uint32_t key_hi = first_key & ~low_mask;  // table and bucket bits: the same for the whole bucket
+      uint32_t* buf[2] = {words, words + smem_capacity};
+      for (int32_t i = threadIdx.x; i < n; i += kOversizeThreads) {
+        const uint2 pr = pairs[seg.x + i];
+        buf[0][i] = ((pr.x & low_mask) << bag_bits) | static_cast<uint32_t>(static_cast<int32_t>(pr.y) - vbase);
+      }
+      __syncthreads();
+      const int total = key_bits + bag_bits;
+      const int np = (total + kDigitBits - 1) / kDigitBits;
+      const int db = np ? (total + np - 1) / np : 0;
+      int side = 0;
+      for (int pass = 0; pass < np; ++pass, side ^= 1)
+        radix_pass_words<kOversizeWarps>(buf[side], buf[side ^ 1], n, pass * db, min(db, total - pass * db), cnt,
+                                         digit_base);
+      const uint32_t bag_mask = bag_bits >= 32 ? 0xffffffffu : ((1u << bag_bits) - 1u);
+      for (int32_t i = threadIdx.x; i < n; i += kOversizeThreads) {
+        const uint32_t x = buf[side][i];
+        kout[seg.x + i] = key_hi | (x >> bag_bits);
+        vout[seg.x + i] = vbase + static_cast<int32_t>(x & bag_mask);
+      }
+      __syncthreads();
+      continue;
+    }
     uint32_t* scratch = reinterpret_cast<uint32_t*>(pairs + seg.x);
     uint32_t* k[2] = {kout + seg.x, scratch};
     int32_t* v[2] = {vout + seg.x, reinterpret_cast<int32_t*>(scratch + n)};
-    const int32_t vbase = static_cast<int32_t>(pairs[seg.x].x >> idx_bits) * B;  // first bag of the bucket's table
+    __syncthreads();  // every thread has read the bucket's first pair
     for (int32_t i = threadIdx.x; i < n; i += kOversizeThreads) {
       const uint2 pr = pairs[seg.x + i];
       k[0][i] = pr.x;
@@ -682,6 +789,29 @@ int bucket_sort_plan(const int32_t* indices, const int32_t* offsets, int64_t T, 
   const size_t rank_smem = static_cast<size_t>(words) * 4 + static_cast<size_t>(kBucketSortCapacity) * 8;
   int dev = 0;
   TBE_CUDA_TRY(cudaGetDevice(&dev));
+  static std::atomic<bool> rank_opted_in[64];
+  if (rank_smem > 48 * 1024 - 64 && dev < 64 && !rank_opted_in[dev].load(std::memory_order_acquire)) {
+    TBE_CUDA_TRY(cudaFuncSetAttribute(bucket_rank_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (1 << kRankCounterBits) * 2 + kBucketSortCapacity * 8));
+    rank_opted_in[dev].store(true, std::memory_order_release);
+  }
+  // the queued-bucket sort keeps a bucket in shared memory when it fits: two 32-bit words per pair in
+  // whatever an SM's shared memory leaves beside the kernel's counters
+  static std::atomic<int> oversize_words[64];
+  int oversize_capacity = dev < 64 ? oversize_words[dev].load(std::memory_order_acquire) : 0;
+  if (dev < 64 && oversize_capacity == 0) {
+    int optin = 0;
+    TBE_CUDA_TRY(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    cudaFuncAttributes attr;
+    TBE_CUDA_TRY(cudaFuncGetAttributes(&attr, oversize_sort_kernel));
+    int dyn = optin - static_cast<int>(attr.sharedSizeBytes) - 256;
+    if (dyn < 0) dyn = 0;
+    TBE_CUDA_TRY(cudaFuncSetAttribute(oversize_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
+    oversize_capacity = dyn / 8 > 0 ? dyn / 8 : -1;  // -1: looked up, nothing fits
+    oversize_words[dev].store(oversize_capacity, std::memory_order_release);
+  }
+  if (oversize_capacity < 0) oversize_capacity = 0;
+  const size_t oversize_smem = static_cast<size_t>(oversize_capacity) * 8;
   const bool wide = g.nb > kFewBuckets;
   constexpr size_t kScatterSmem = kScatterTile * sizeof(uint2) + 3 * kFewBuckets * sizeof(int32_t);
   constexpr size_t kScatterSmemWide = kScatterTileWide * sizeof(uint2) + 3 * kMaxBuckets * sizeof(int32_t);
@@ -726,9 +856,9 @@ int bucket_sort_plan(const int32_t* indices, const int32_t* offsets, int64_t T, 
     int bag_bits = 0;
     while ((1ll << bag_bits) < B) ++bag_bits;
     KernelTimer timer("oversize_sort_kernel", stream);
-    oversize_sort_kernel<<<static_cast<unsigned>(blocks), kOversizeThreads, 0, stream>>>(
+    oversize_sort_kernel<<<static_cast<unsigned>(blocks), kOversizeThreads, oversize_smem, stream>>>(
         pairs, ws.keys, ws.vals, g.shift, bag_bits, layout.idx_bits, static_cast<int32_t>(B), queue_count,
-        ws.oversize, qcap);
+        ws.oversize, qcap, oversize_capacity);
   }
   TBE_CHECK_LAUNCH("oversize_sort_kernel");
   return TBE_OK;

@@ -57,7 +57,7 @@ class LXUCachedEmbeddingBags(nn.Module):
     ``ways``-way set-associative HBM cache of ``cache_rows`` rows; fused exact SGD."""
 
     def __init__(self, num_tables, num_embeddings, embedding_dim, cache_rows, ways=4, policy="lru",
-                 learning_rate=0.01, fp16=False, pooling_mode="sum"):
+                 learning_rate=0.01, fp16=False, pooling_mode="sum", deferred_writeback=False):
         super().__init__()
         assert policy in _POLICY and pooling_mode in ("sum", "mean")
         assert ways in (1, 2, 4, 8, 16, 32) and cache_rows % ways == 0
@@ -83,6 +83,15 @@ class LXUCachedEmbeddingBags(nn.Module):
         self._stats = torch.zeros(5, dtype=torch.int32, device=device)
         self._locations = None
         self._workspace = None
+        # deferred write-backs (optional): dirty victims are staged in HBM by the prefetch and carried to
+        # the host table on a side stream while the lookup runs; the next prefetch (and flush) wait for
+        # them.  Off by default: SM-issued traffic to mapped host memory shares one ~25 GB/s link budget,
+        # so the deferred stores only move the time from the fill kernel into the lookup they overlap.
+        self.deferred_writeback = deferred_writeback
+        self._wb_rows = None
+        self._wb_ids = None
+        self._wb_stream = None
+        self._wb_done = None
         self.totals = {"lookups": 0, "hit_lookups": 0, "rows": 0, "hit_rows": 0, "fetched": 0, "uncached": 0}
 
     def batch_of(self, offsets):
@@ -102,14 +111,41 @@ class LXUCachedEmbeddingBags(nn.Module):
         if self._locations is None or self._locations.numel() < N:
             self._locations = torch.empty(max(N, 1), dtype=torch.int32, device=dev)
         self.step += 1
+        stage = min(N, self.cache_rows.size(0))
+        if self.deferred_writeback and stage > 0:
+            if self._wb_rows is None or self._wb_rows.size(0) < stage:
+                self._wait_writeback(dev)  # the side stream may still be reading the old staging buffer
+                self._wb_rows = torch.empty((stage, self.embedding_dim), dtype=w.dtype, device=dev)
+                self._wb_ids = torch.empty(stage, dtype=torch.int32, device=dev)
+            if self._wb_stream is None:
+                self._wb_stream = torch.cuda.Stream(dev, priority=-1)
+        defer = self.deferred_writeback and stage > 0
         with torch.cuda.device(dev):
+            main = torch.cuda.current_stream(dev)
+            self._wait_writeback(dev)  # this step's fetches must see the previous step's write-backs
             _lib.call("tbe_cache_prefetch", self.cache_rows.data_ptr(), self.tags.data_ptr(), self.last_use.data_ptr(),
                       self.use_count.data_ptr(), self.dirty.data_ptr(), w.data_ptr(), self.table_offsets.data_ptr(),
                       indices.data_ptr(), offsets.data_ptr(), self._locations.data_ptr(), self._stats.data_ptr(),
                       self.num_tables, self.batch_of(offsets), self.embedding_dim, N, w.size(0), self.num_sets,
                       self.ways, tbe_ext._DTYPES[w.dtype], _POLICY[self.policy], self.step,
+                      self._wb_rows.data_ptr() if defer else None, self._wb_ids.data_ptr() if defer else None,
                       self._workspace.data_ptr(), self._workspace.numel(), tbe_ext._stream(dev))
+            if defer and N > 0:
+                filled = torch.cuda.Event()
+                filled.record(main)
+                self._wb_stream.wait_event(filled)
+                _lib.call("tbe_cache_writeback", self._wb_rows.data_ptr(), self._wb_ids.data_ptr(),
+                          self._stats.data_ptr(), w.data_ptr(), self.embedding_dim, tbe_ext._DTYPES[w.dtype],
+                          ctypes.c_void_p(self._wb_stream.cuda_stream))
+                self._wb_done = torch.cuda.Event()
+                self._wb_done.record(self._wb_stream)
         self._last_n = N
+
+    def _wait_writeback(self, device):
+        """The current stream waits for the write-backs staged by the last prefetch."""
+        if self._wb_done is not None:
+            torch.cuda.current_stream(device).wait_event(self._wb_done)
+            self._wb_done = None
 
     def forward(self, indices, offsets):
         return _CachedLookup.apply(self._anchor, self, indices, offsets)
@@ -127,6 +163,7 @@ class LXUCachedEmbeddingBags(nn.Module):
         """Writes every dirty cached row back to the host table (call before reading the table)."""
         w = self.embedding_weights
         with torch.cuda.device(w.device):
+            self._wait_writeback(w.device)
             _lib.call("tbe_cache_flush", self.cache_rows.data_ptr(), w.data_ptr(), self.tags.data_ptr(),
                       self.dirty.data_ptr(), self.cache_rows.size(0), self.embedding_dim, tbe_ext._DTYPES[w.dtype],
                       tbe_ext._stream(w.device))

@@ -43,7 +43,10 @@ def _workspace(device, nbytes):
     with _ws_lock:
         buf = _workspaces.get(key)
         if buf is None or buf.numel() < nbytes:
-            buf = torch.empty(int(nbytes * 1.25) + 4096, dtype=torch.uint8, device=device)
+            buf = None
+            _workspaces.pop(key, None)  # release the old buffer before asking for a larger one
+            headroom = 1.25 if nbytes < (1 << 30) else 1.0  # small batches vary in size; huge ones take what they need
+            buf = torch.empty(int(nbytes * headroom) + 4096, dtype=torch.uint8, device=device)
             _workspaces[key] = buf
         return buf
 

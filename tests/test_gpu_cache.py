@@ -54,7 +54,8 @@ def test_slot_bookkeeping_matches_cpu_model(cuda_device, policy, ways):
 
 @pytest.mark.parametrize("fp16", [False, True])
 @pytest.mark.parametrize("pooling", ["sum", "mean"])
-def test_cached_module_is_transparent(cuda_device, fp16, pooling):
+@pytest.mark.parametrize("deferred", [False, True])
+def test_cached_module_is_transparent(cuda_device, fp16, pooling, deferred):
     """Several fwd + SGD steps through a small cache (evictions, write-backs, uncached rows) give the
     outputs and the final table of the uncached device-resident module and of the oracle."""
     T, E, D, B, Lmax, lr = 3, 60, 32, 8, 6, 0.05
@@ -64,7 +65,7 @@ def test_cached_module_is_transparent(cuda_device, fp16, pooling):
                                           pooling_mode=pooling).cuda()
     plain.embedding_weights.data.uniform_(-1, 1)
     cached = LXUCachedEmbeddingBags(T, E, D, cache_rows=16, ways=4, policy="lru", learning_rate=lr, fp16=fp16,
-                                    pooling_mode=pooling)
+                                    pooling_mode=pooling, deferred_writeback=deferred)
     cached.embedding_weights.data.copy_(plain.embedding_weights.data)
     w_ref = plain.embedding_weights.detach().cpu().clone()
     to = [t * E for t in range(T)]
