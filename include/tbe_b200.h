@@ -68,7 +68,9 @@ TBE_API int64_t tbe_library_launch_count(void);
  *   long_segment                                 run length above which a run gets a CTA of its own
  *   bwd_sort                                     1: always linearize + device radix sort for the backward plan
  *   sort_bucket                                  wanted mean bucket size of the table-segmented sort
- *   split_runs                                   1: one CTA per queued long run, never several */
+ *   split_runs                                   1: one CTA per queued long run, never several
+ *   bwd_stride                                   backward apply hands out its tiles 1: with a fixed stride, 2: by a ticket
+ *                                                counter (default: tickets once the pooled gradient exceeds a third of L2) */
 TBE_API int tbe_set_tuning(const char* name, int value);
 
 /* Per-launch timing for benchmarks: while enabled, every kernel launch of this library

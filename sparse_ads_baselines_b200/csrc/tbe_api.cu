@@ -19,7 +19,7 @@ std::atomic<int64_t> g_library_launches{0};
 std::atomic<int> g_tuning[kTuneCount];
 const char* const kTuningNames[kTuneCount] = {"fwd_unroll", "fwd_threads", "bwd_threads", "bwd_unroll",
                                               "long_segment", "fwd_blocks_per_sm", "bwd_blocks_per_sm", "bwd_vpl",
-                                              "bwd_sort", "sort_bucket", "split_runs"};
+                                              "bwd_sort", "sort_bucket", "split_runs", "bwd_stride"};
 }  // namespace
 
 namespace {
@@ -80,6 +80,18 @@ int device_sm_count() {
   int v = cache[dev].load(std::memory_order_relaxed);
   if (v == 0) {
     if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    cache[dev].store(v, std::memory_order_relaxed);
+  }
+  return v;
+}
+
+int64_t device_l2_bytes() {
+  static std::atomic<int> cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 126ll << 20;
+  int v = cache[dev].load(std::memory_order_relaxed);
+  if (v == 0) {
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrL2CacheSize, dev) != cudaSuccess || v <= 0) v = 126 << 20;
     cache[dev].store(v, std::memory_order_relaxed);
   }
   return v;

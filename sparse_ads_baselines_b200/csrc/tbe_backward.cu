@@ -240,6 +240,7 @@ struct BwdArgs {
   float lr, eps;
   uint64_t sr_seed, sr_offset;
   const float* bag_g2;       // approximate Adagrad: squared gradient norm of every bag
+  int32_t* tile_ticket;      // run_kernel: tiles handed out so far beyond every warp's first (null: fixed stride)
   // long runs cut into parts (0 = off): a part is split_len entries (the last one up to twice that)
   int32_t split_len, max_parts;
   int4* part_list;           // dense list of parts: {first entry, end entry, list index of the run's first part, parts of the run}
@@ -426,10 +427,20 @@ __global__ void __launch_bounds__(kBwdThreads, 4) run_kernel(const BwdArgs a) {
   const int sub = lane & (lpr - 1);
   const int slot = lane >> lpr_log2;
   const int N = a.N;
-  const int64_t ntiles = (static_cast<int64_t>(N) + 31) >> 5;
-  const int64_t wstride = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
-  int64_t tile = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int32_t ntiles = static_cast<int32_t>((static_cast<int64_t>(N) + 31) >> 5);  // N < 2^31
+  // A warp starts on the tile of its own number and then takes whichever tile is next on the ticket
+  // counter: tiles differ a lot in cost (a tile inside a long run costs nothing, one with 32 runs 32
+  // row updates), and with a fixed stride the warps with the dearest tiles would finish last.
+  const int32_t wstride = static_cast<int32_t>(gridDim.x * (blockDim.x >> 5));
+  const bool ticketed = a.tile_ticket != nullptr;
+  int32_t tile = static_cast<int32_t>(blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5));
   if (tile >= ntiles) return;
+  int32_t ntile = tile + wstride;
+  if (ticketed) {
+    int32_t tk = 0;
+    if (lane == 0) tk = atomicAdd(a.tile_ticket, 1);
+    ntile = wstride + __shfl_sync(kFullMask, tk, 0);
+  }
   const uint32_t row_bytes = static_cast<uint32_t>(a.D) * static_cast<uint32_t>(sizeof(T));
   const uint32_t* __restrict__ keys = a.keys;
   const int32_t* __restrict__ vals = a.vals;
@@ -448,10 +459,11 @@ __global__ void __launch_bounds__(kBwdThreads, 4) run_kernel(const BwdArgs a) {
   // gradient row offsets are kept in units of VB bytes so that they fit one 32-bit shuffle
   const uint32_t sb_units = static_cast<uint32_t>(a.stride_b * static_cast<int64_t>(sizeof(T)) / VB);
   const uint32_t st_units = static_cast<uint32_t>(a.stride_t * static_cast<int64_t>(sizeof(T)) / VB);
-  Philox rng(a.sr_seed, static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x, a.sr_offset);
+  // the random stream belongs to the (tile, lane), not to the thread: the result does not depend on
+  // which warp came to process a tile
+  Philox rng(a.sr_seed, static_cast<uint64_t>(tile) * 32 + lane, a.sr_offset);
   const uint64_t keep = l2_policy_evict_last(), streaming = l2_policy_evict_first();
-  // a lane group owns the runs that start in its own lanes of the tile
-  const unsigned own_lanes = (lpr_log2 == 5) ? kFullMask : (((1u << lpr) - 1u) << (slot << lpr_log2));
+  const int ngroups = 32 >> lpr_log2;  // lane groups of the warp; the tile's runs are dealt out to them in turn
 
   // offset (in VB-byte units) of the gradient row of a bag, and 1/L of the bag for mean pooling
   auto grad_units = [&](uint32_t bag, acc_t* scale) -> uint32_t {
@@ -466,12 +478,15 @@ __global__ void __launch_bounds__(kBwdThreads, 4) run_kernel(const BwdArgs a) {
 
   Tile cur = load_tile(keys, vals, tile, lane, N);
   while (true) {
-    const int64_t ntile = tile + wstride;
     Tile nxt = cur;
-    if (ntile < ntiles) nxt = load_tile(keys, vals, ntile, lane, N);
+    int32_t ticket = 0;  // (requested now, read at the end of the tile)
+    if (ntile < ntiles) {
+      nxt = load_tile(keys, vals, ntile, lane, N);
+      if (ticketed && lane == 0) ticket = atomicAdd(a.tile_ticket, 1);
+    }
 
     // ---- per entry, all lanes at once
-    const int p0 = static_cast<int>(tile << 5);
+    const int p0 = tile << 5;
     const int nvalid = min(32, N - p0);
     const bool valid = lane < nvalid;
     uint32_t prev = __shfl_up_sync(kFullMask, cur.key, 1);
@@ -504,8 +519,18 @@ __global__ void __launch_bounds__(kBwdThreads, 4) run_kernel(const BwdArgs a) {
       my_state = a.state[my_row] + x;
       my_scale = static_cast<acc_t>(approx_step(a, my_state));
     }
-    unsigned mine = smask & own_lanes;
-    const int rounds = __reduce_max_sync(kFullMask, __popc(mine));
+    // the k-th run of the tile goes to lane group k mod ngroups: every group gets its share whatever
+    // the lengths of the runs are (runs dealt out by the lanes they start in would leave a group with
+    // one long run idle while its neighbour works through eight short ones)
+    unsigned mine = smask;
+    if (ngroups > 1) {
+      const int turn = __popc(smask & ((1u << lane) - 1u)) & (ngroups - 1);
+      for (int g = 0; g < ngroups; ++g) {
+        const unsigned m = __ballot_sync(kFullMask, is_start && turn == g);
+        if (g == slot) mine = m;
+      }
+    }
+    const int rounds = (__popc(smask) + ngroups - 1) >> (5 - lpr_log2);
 
     // ---- per run
     for (int k = 0; k < rounds; k += SEGS) {
@@ -650,7 +675,9 @@ __global__ void __launch_bounds__(kBwdThreads, 4) run_kernel(const BwdArgs a) {
 
     tile = ntile;
     if (tile >= ntiles) break;
+    ntile = ticketed ? wstride + __shfl_sync(kFullMask, ticket, 0) : tile + wstride;
     cur = nxt;
+    if (SR) rng = Philox(a.sr_seed, static_cast<uint64_t>(tile) * 32 + lane, a.sr_offset);
   }
 }
 
@@ -1165,6 +1192,16 @@ int exact_backward(int opt, const void* grad, int64_t stride_b, int64_t stride_t
   a.vals = ws.vals;
   a.long_list = ws.long_list;
   a.long_count = ws.counters + 1;
+  // Tickets keep all warps on neighbouring tiles of the sorted order, i.e. on one table's slice of the
+  // pooled gradient at a time; that pays once the gradient no longer sits in L2 as a whole (config 5:
+  // 1 GB of gradient, run_kernel 10.7 -> 7.6 ms).  A gradient that fits anyway is a little faster with
+  // the fixed stride (no ticket traffic).
+  {
+    const int mode = tuning(kTuneBwdStride);
+    const int64_t grad_bytes = B * T * D * elem_size(dtype);
+    const bool tickets = mode == 2 || (mode != 1 && grad_bytes * 3 > device_l2_bytes());
+    a.tile_ticket = tickets ? ws.counters + 5 : nullptr;  // cleared with the other counters above
+  }
   a.offsets = offsets;
   a.table_offsets = table_offsets;
   a.idx_bits = layout.idx_bits;

@@ -35,6 +35,7 @@ enum Tuning {
   kTuneBwdSort,     // 0: two-level bucket sort when the batch suits it, 1: always the device radix sort
   kTuneSortBucket,  // wanted mean bucket size of the two-level sort (0: default)
   kTuneSplitRuns,   // 1: never cut long runs into parts (one CTA per queued run)
+  kTuneBwdStride,   // run_kernel's warps walk the tiles 1: with a fixed stride, 2: by ticket, 0: by the gradient's size
   kTuneCount
 };
 
@@ -62,6 +63,7 @@ enum Tuning {
   } while (0)
 
 int device_sm_count();
+int64_t device_l2_bytes();
 
 // Optional per-launch timing: when enabled (tbe_kernel_timing_enable), every launch site brackets
 // its kernel with two CUDA events on the launch stream; tbe_kernel_timing_read sums them per name.

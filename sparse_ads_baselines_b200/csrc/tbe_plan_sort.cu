@@ -24,13 +24,17 @@
 //                              sort of the position-ordered input gives, and independent of how the
 //                              atomics of any step were served.  A bucket larger than the CTA's
 //                              capacity, or with a hot row, is queued instead ...
-//   4. oversize_sort_kernel  : ... and sorted by a 1024-thread CTA with stable 8-bit radix passes
-//                              through global memory, first on the bag id, then on the index bits.
-//                              Skewed batches, where a few hot rows put most of a table in one
-//                              bucket, land here; normally the queue is empty.
+//   4. oversize_sort_kernel  : ... and sorted by a cluster of eight CTAs with stable radix passes on
+//                              (index bits, bag id) in their joint shared memory.  Skewed batches,
+//                              where a few hot rows put most of a table in one bucket, land here;
+//                              normally the queue is empty.
+#include <cooperative_groups.h>
+
 #include <atomic>
 
 #include "tbe_plan.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace tbe {
 
@@ -46,8 +50,15 @@ constexpr int kRankBits = 14;                                   // most index bi
 constexpr int kRankCounterBits = 13;                            // level 2 keeps at most 8192 counters per bucket
 constexpr int kRankMaxGroup = kBucketSortMaxGroup;              // most pairs one counter may collect
 static_assert(kBucketSortCapacity <= 2048 && kRankMaxGroup < 1024, "packing of bucket_rank_kernel's `where`");
-constexpr int kOversizeThreads = 1024;
+constexpr int kOversizeThreads = 512;
 constexpr int kOversizeWarps = kOversizeThreads / 32;
+constexpr int kSortCluster = 8;     // CTAs (one cluster) that sort a queued bucket together
+constexpr int kSortBlock = 8192;    // pairs of the bucket a CTA of the cluster holds at most
+constexpr int kSortDigitBits = 9;   // the in-cluster passes look at up to 9 bits: one digit per thread
+constexpr int kSortDigits = 1 << kSortDigitBits;
+constexpr size_t kSortSmem = (2 * kSortBlock + kOversizeWarps * (kSortDigits / 2) + 2 * kSortDigits) * sizeof(uint32_t);
+static_assert(kSortDigits <= kOversizeThreads && kSortCluster * kSortBlock <= 65536 && kSortBlock % 32 == 0,
+              "one digit per thread; positions below 2^16 for the division by multiplication");
 constexpr int kMaxDigits = 128;             // radix passes look at up to 7 bits
 constexpr int kDigitBits = 7;
 constexpr int kFewBuckets = 1024;           // buckets per table the narrow kernel variants hold in shared memory
@@ -592,151 +603,173 @@ __device__ __forceinline__ void radix_pass(const uint32_t* sk, const int32_t* sv
   __syncthreads();
 }
 
-// The same stable pass over n 32-bit words (shared memory to shared memory).  (Finding the lanes with
-// equal digits with one match instruction instead of `dbits` ballots was measured and is slower here.)
-template <int W>
-__device__ __forceinline__ void radix_pass_words(const uint32_t* src, uint32_t* dst, int32_t n, int sh, int dbits,
-                                                 int32_t* cnt, int32_t* digit_base) {
-  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-  const int nd = 1 << dbits;
-  const uint32_t mask = static_cast<uint32_t>(nd - 1);
-  int32_t ca, cb;
-  warp_share(0, n, w, W, &ca, &cb);
-  int32_t* my_cnt = cnt + w * kMaxDigits;
-  for (int i = lane; i < nd; i += 32) my_cnt[i] = 0;
-  __syncwarp();
-  for (int32_t p = ca + lane; p < cb; p += 32) atomicAdd(&my_cnt[(src[p] >> sh) & mask], 1);
-  __syncthreads();
-  for (int d = threadIdx.x; d < nd; d += W * 32) {
-    int32_t run = 0;
-#pragma unroll 8
-    for (int w2 = 0; w2 < W; ++w2) {
-      const int32_t c = cnt[w2 * kMaxDigits + d];
-      cnt[w2 * kMaxDigits + d] = run;
-      run += c;
-    }
-    digit_base[d] = run;
-  }
-  __syncthreads();
-  if (w == 0) {  // exclusive scan of the per-digit totals
-    constexpr int kPer = kMaxDigits / 32;
-    int32_t v[kPer];
-    int32_t sum = 0;
-#pragma unroll
-    for (int j = 0; j < kPer; ++j) {
-      const int d = lane * kPer + j;
-      v[j] = d < nd ? digit_base[d] : 0;
-      sum += v[j];
-    }
-    int32_t incl = sum;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int32_t up = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += up;
-    }
-    int32_t run = incl - sum;
-#pragma unroll
-    for (int j = 0; j < kPer; ++j) {
-      const int d = lane * kPer + j;
-      if (d < nd) digit_base[d] = run;
-      run += v[j];
-    }
-  }
-  __syncthreads();
-  for (int32_t p0 = ca; p0 < cb; p0 += 32) {
-    const int32_t p = p0 + lane;
-    const bool valid = p < cb;
-    const uint32_t x = valid ? src[p] : 0u;
-    const uint32_t d = (x >> sh) & mask;
-    uint32_t peers = __ballot_sync(0xffffffffu, valid);
-    for (int bit = 0; bit < dbits; ++bit) {
-      const bool one = (d >> bit) & 1u;
-      const uint32_t set = __ballot_sync(0xffffffffu, one);
-      peers &= one ? set : ~set;
-    }
-    const int r = __popc(peers & ((1u << lane) - 1u));
-    if (valid) dst[digit_base[d] + my_cnt[d] + r] = x;
-    __syncwarp();
-    if (valid && r == 0) my_cnt[d] += __popc(peers);
-    __syncwarp();
-  }
-  __syncthreads();
-}
-
 // Buckets too large for bucket_rank_kernel (or with a hot row): least-significant-digit radix sort on
-// (index bits, bag id within the table), one 1024-thread CTA per queued bucket.  A fixed grid walks
-// the queue, so an empty queue costs one launch.
+// (index bits, bag id within the table).  A fixed grid walks the queue, so an empty queue costs one
+// launch.
 //
-// When the bucket fits (the usual case: the first bucket of a skewed table holds ~25,000 pairs) the
-// sort runs entirely in shared memory: a pair's index bits and its bag id within the table are packed
-// into one 32-bit word, index bits on top, so that ascending words ARE the order by (index, bag); two
-// word buffers of `smem_capacity` entries ping-pong through the passes and keys and bag ids are
-// rebuilt on the way out.  Larger buckets (or more than 32 bits) take the passes through global
-// memory: the bucket's pairs are first split into the output arrays, the passes then ping-pong
-// between those and the bucket's own stretch of the pair array, which is free by then.
-__global__ void __launch_bounds__(kOversizeThreads) oversize_sort_kernel(uint2* pairs, uint32_t* kout, int32_t* vout,
-                                                                         int key_bits, int bag_bits, int idx_bits,
-                                                                         int32_t B,
-                                                                         const int32_t* __restrict__ queue_count,
-                                                                         const int2* __restrict__ queue,
-                                                                         int queue_cap, int smem_capacity) {
-  extern __shared__ uint32_t words[];  // 2 * smem_capacity
-  __shared__ int32_t cnt[kOversizeWarps * kMaxDigits];
-  __shared__ int32_t digit_base[kMaxDigits];
+// A queued bucket is sorted by a thread-block CLUSTER of four or eight CTAs in their joint shared
+// memory (the first bucket of a skewed table holds ~25,000 pairs; one CTA needs four times longer
+// for it than the rest of the plan takes).  A pair's index bits and its bag id within the table are
+// packed into one 32-bit word, index bits on top, so that ascending words ARE the order by (index,
+// bag).  CTA c of the cluster holds positions [c * per, (c + 1) * per) of the bucket in each of two
+// word buffers.  One pass: every warp counts the digits of its share of the CTA's block; the CTAs
+// read each other's per-digit totals through distributed shared memory, which gives every (digit,
+// CTA, warp) its first output position in the bucket; the warps then rank equal digits with ballots
+// and store each word into the buffer of whichever CTA owns its new position (a remote shared-memory
+// store).  Two cluster barriers per pass; keys and bag ids are rebuilt on the way out.
+//
+// A bucket beyond (CTAs of the cluster) * kSortBlock pairs (or more than 32 bits of index + bag) is sorted by
+// the cluster's first CTA alone with passes through global memory: the bucket's pairs are first
+// split into the output arrays, the passes then ping-pong between those and the bucket's own stretch
+// of the pair array, which is free by then.
+__global__ void __launch_bounds__(kOversizeThreads, 2)
+    oversize_sort_kernel(uint2* pairs, uint32_t* kout, int32_t* vout, int key_bits, int bag_bits, int idx_bits,
+                         int32_t B, const int32_t* __restrict__ queue_count, const int2* __restrict__ queue,
+                         int queue_cap) {
+  extern __shared__ uint32_t sort_smem[];  // two word buffers of kSortBlock, then the counters
+  uint32_t* cnt = sort_smem + 2 * kSortBlock;  // [warp][digit / 2]; [warp][kMaxDigits] of 32 bits for the global passes
+  int32_t* tot = reinterpret_cast<int32_t*>(cnt + kOversizeWarps * (kSortDigits / 2));  // this CTA's words per digit
+  int32_t* digit_base = tot + kSortDigits;
+  __shared__ int32_t warp_tot[kOversizeWarps];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = static_cast<int>(cluster.block_rank());
+  const int csize = static_cast<int>(cluster.num_blocks());  // 4 or 8 (chosen at launch), at most kSortCluster
+  const int cid = blockIdx.x / csize, nclusters = gridDim.x / csize;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const int count = min(*queue_count, queue_cap);
-  const int vp = (bag_bits + kDigitBits - 1) / kDigitBits, kp = (key_bits + kDigitBits - 1) / kDigitBits;
-  const int vd = vp ? (bag_bits + vp - 1) / vp : 0, kd = kp ? (key_bits + kp - 1) / kp : 0;
-  for (int q = blockIdx.x; q < count; q += gridDim.x) {
+  for (int q = cid; q < count; q += nclusters) {  // (the same buckets for every CTA of a cluster)
     const int2 seg = queue[q];
     const int32_t n = seg.y - seg.x;
     const uint32_t first_key = pairs[seg.x].x;
     const int32_t vbase = static_cast<int32_t>(first_key >> idx_bits) * B;  // first bag of the bucket's table
-    if (n <= smem_capacity && key_bits + bag_bits <= 32) {
+    if (n <= csize * kSortBlock && key_bits + bag_bits <= 32) {
+      // block length: a multiple of 32, at most kSortBlock; position / per by multiplication (exact
+      // below 2^16 positions for per < 2^16)
+      const int32_t per = (((n + csize - 1) / csize) + 31) & ~31;
+      const uint32_t per_magic = static_cast<uint32_t>(((1ull << 32) + per - 1) / per);
+      const int32_t lo = rank * per;
+      const int32_t m = max(0, min(per, n - lo));  // words this CTA holds
       const uint32_t low_mask = key_bits >= 32 ? 0xffffffffu : ((1u << key_bits) - 1u);
       const uint32_t key_hi = first_key & ~low_mask;  // table and bucket bits: the same for the whole bucket
-      uint32_t* buf[2] = {words, words + smem_capacity};
-      for (int32_t i = threadIdx.x; i < n; i += kOversizeThreads) {
-        const uint2 pr = pairs[seg.x + i];
-        buf[0][i] = ((pr.x & low_mask) << bag_bits) | static_cast<uint32_t>(static_cast<int32_t>(pr.y) - vbase);
+      for (int32_t i = threadIdx.x; i < m; i += kOversizeThreads) {
+        const uint2 pr = pairs[seg.x + lo + i];
+        sort_smem[i] = ((pr.x & low_mask) << bag_bits) | static_cast<uint32_t>(static_cast<int32_t>(pr.y) - vbase);
       }
       __syncthreads();
       const int total = key_bits + bag_bits;
-      const int np = (total + kDigitBits - 1) / kDigitBits;
+      const int np = (total + kSortDigitBits - 1) / kSortDigitBits;
       const int db = np ? (total + np - 1) / np : 0;
+      int32_t ca, cb;
+      warp_share(0, m, w, kOversizeWarps, &ca, &cb);
+      // per-warp digit counters, two 16-bit counters to a word (a CTA's block is below 2^16 words)
+      uint32_t* my_cnt = cnt + w * (kSortDigits / 2);
       int side = 0;
-      for (int pass = 0; pass < np; ++pass, side ^= 1)
-        radix_pass_words<kOversizeWarps>(buf[side], buf[side ^ 1], n, pass * db, min(db, total - pass * db), cnt,
-                                         digit_base);
-      const uint32_t bag_mask = bag_bits >= 32 ? 0xffffffffu : ((1u << bag_bits) - 1u);
-      for (int32_t i = threadIdx.x; i < n; i += kOversizeThreads) {
-        const uint32_t x = buf[side][i];
-        kout[seg.x + i] = key_hi | (x >> bag_bits);
-        vout[seg.x + i] = vbase + static_cast<int32_t>(x & bag_mask);
+      for (int pass = 0; pass < np; ++pass, side ^= 1) {
+        const uint32_t* src = sort_smem + side * kSortBlock;
+        uint32_t* dst = sort_smem + (side ^ 1) * kSortBlock;
+        const int sh = pass * db, dbits = min(db, total - sh);
+        const int nd = 1 << dbits;
+        const uint32_t mask = static_cast<uint32_t>(nd - 1);
+        for (int i = lane; i < (nd + 1) / 2; i += 32) my_cnt[i] = 0u;
+        __syncwarp();
+        for (int32_t p = ca + lane; p < cb; p += 32) {
+          const uint32_t d = (src[p] >> sh) & mask;
+          atomicAdd(&my_cnt[d >> 1], 1u << ((d & 1u) * 16));
+        }
+        __syncthreads();
+        if (threadIdx.x < (nd + 1) / 2) {  // counts -> first place of every warp among this CTA's words of a digit
+          uint32_t run = 0;  // both digits of the word at once
+#pragma unroll
+          for (int w2 = 0; w2 < kOversizeWarps; ++w2) {
+            const uint32_t c = cnt[w2 * (kSortDigits / 2) + threadIdx.x];
+            cnt[w2 * (kSortDigits / 2) + threadIdx.x] = run;
+            run += c;
+          }
+          tot[2 * threadIdx.x] = static_cast<int32_t>(run & 0xffffu);
+          tot[2 * threadIdx.x + 1] = static_cast<int32_t>(run >> 16);
+        }
+        cluster.sync();  // every CTA's totals are in place
+        int32_t all = 0, before = 0;
+        if (threadIdx.x < nd) {
+#pragma unroll
+          for (int c = 0; c < kSortCluster; ++c) {
+            const int32_t t = c < csize ? cluster.map_shared_rank(tot, c)[threadIdx.x] : 0;
+            all += t;
+            if (c < rank) before += t;
+          }
+        }
+        // words of smaller digits in the whole bucket, plus words of this digit in the CTAs in front
+        const int32_t smaller = cta_exclusive_scan(all, warp_tot, threadIdx.x < ((nd + 31) & ~31));
+        if (threadIdx.x < nd) digit_base[threadIdx.x] = smaller + before;
+        __syncthreads();
+        // (Ranking equal digits once, in the counting loop, and keeping each word's rank for this loop was
+        // measured and is slower: the ballots cost more there than the conflicting shared-memory adds.)
+        for (int32_t p0 = ca; p0 < cb; p0 += 32) {
+          const int32_t p = p0 + lane;
+          const bool valid = p < cb;
+          const uint32_t x = valid ? src[p] : 0u;
+          const uint32_t d = (x >> sh) & mask;
+          uint32_t peers = __ballot_sync(0xffffffffu, valid);
+#pragma unroll
+          for (int bit = 0; bit < kSortDigitBits; ++bit) {  // (bits beyond dbits are zero in every lane: no effect)
+            const uint32_t set = __ballot_sync(0xffffffffu, (d >> bit) & 1u);
+            peers &= ((d >> bit) & 1u) ? set : ~set;
+          }
+          const int r = __popc(peers & ((1u << lane) - 1u));
+          const int half = (d & 1u) * 16;
+          if (valid) {
+            // new position in the bucket
+            const uint32_t g = static_cast<uint32_t>(digit_base[d]) + ((my_cnt[d >> 1] >> half) & 0xffffu) + r;
+            const uint32_t owner = __umulhi(g, per_magic);
+            cluster.map_shared_rank(dst, owner)[g - owner * static_cast<uint32_t>(per)] = x;
+          }
+          __syncwarp();
+          if (valid && r == 0) atomicAdd(&my_cnt[d >> 1], static_cast<uint32_t>(__popc(peers)) << half);
+          __syncwarp();
+        }
+        cluster.sync();  // every word of the pass has landed; the totals may be overwritten
       }
-      __syncthreads();
+      const uint32_t* fin = sort_smem + side * kSortBlock;
+      const uint32_t bag_mask = bag_bits >= 32 ? 0xffffffffu : ((1u << bag_bits) - 1u);
+      for (int32_t i = threadIdx.x; i < m; i += kOversizeThreads) {
+        const uint32_t x = fin[i];
+        kout[seg.x + lo + i] = key_hi | (x >> bag_bits);
+        vout[seg.x + lo + i] = vbase + static_cast<int32_t>(x & bag_mask);
+      }
+      __syncthreads();  // the next bucket is loaded over these buffers
       continue;
     }
+    if (rank != 0) continue;
+    const int vp = (bag_bits + kDigitBits - 1) / kDigitBits, kp = (key_bits + kDigitBits - 1) / kDigitBits;
+    const int vd = vp ? (bag_bits + vp - 1) / vp : 0, kd = kp ? (key_bits + kp - 1) / kp : 0;
     uint32_t* scratch = reinterpret_cast<uint32_t*>(pairs + seg.x);
-    uint32_t* k[2] = {kout + seg.x, scratch};
-    int32_t* v[2] = {vout + seg.x, reinterpret_cast<int32_t*>(scratch + n)};
+    uint32_t *k_src = kout + seg.x, *k_dst = scratch;
+    int32_t *v_src = vout + seg.x, *v_dst = reinterpret_cast<int32_t*>(scratch + n);
     __syncthreads();  // every thread has read the bucket's first pair
     for (int32_t i = threadIdx.x; i < n; i += kOversizeThreads) {
       const uint2 pr = pairs[seg.x + i];
-      k[0][i] = pr.x;
-      v[0][i] = static_cast<int32_t>(pr.y);
+      k_src[i] = pr.x;
+      v_src[i] = static_cast<int32_t>(pr.y);
     }
     __syncthreads();
-    int side = 0;
-    for (int pass = 0; pass < vp; ++pass, side ^= 1)
-      radix_pass<kOversizeWarps, true>(k[side], v[side], k[side ^ 1], v[side ^ 1], n, vbase, pass * vd,
-                                       min(vd, bag_bits - pass * vd), cnt, digit_base);
-    for (int pass = 0; pass < kp; ++pass, side ^= 1)
-      radix_pass<kOversizeWarps, false>(k[side], v[side], k[side ^ 1], v[side ^ 1], n, vbase, pass * kd,
-                                        min(kd, key_bits - pass * kd), cnt, digit_base);
-    if (side == 1) {  // an odd number of passes ends in the scratch
+    auto swap_sides = [&]() {
+      uint32_t* kt = k_src;
+      k_src = k_dst;
+      k_dst = kt;
+      int32_t* vt = v_src;
+      v_src = v_dst;
+      v_dst = vt;
+    };
+    for (int pass = 0; pass < vp; ++pass, swap_sides())
+      radix_pass<kOversizeWarps, true>(k_src, v_src, k_dst, v_dst, n, vbase, pass * vd, min(vd, bag_bits - pass * vd),
+                                       reinterpret_cast<int32_t*>(cnt), digit_base);
+    for (int pass = 0; pass < kp; ++pass, swap_sides())
+      radix_pass<kOversizeWarps, false>(k_src, v_src, k_dst, v_dst, n, vbase, pass * kd, min(kd, key_bits - pass * kd),
+                                        reinterpret_cast<int32_t*>(cnt), digit_base);
+    if (k_src != kout + seg.x) {  // an odd number of passes ends in the scratch
       for (int32_t i = threadIdx.x; i < n; i += kOversizeThreads) {
-        k[0][i] = k[1][i];
-        v[0][i] = v[1][i];
+        k_dst[i] = k_src[i];
+        v_dst[i] = v_src[i];
       }
       __syncthreads();
     }
@@ -795,23 +828,35 @@ int bucket_sort_plan(const int32_t* indices, const int32_t* offsets, int64_t T, 
                                       (1 << kRankCounterBits) * 2 + kBucketSortCapacity * 8));
     rank_opted_in[dev].store(true, std::memory_order_release);
   }
-  // the queued-bucket sort keeps a bucket in shared memory when it fits: two 32-bit words per pair in
-  // whatever an SM's shared memory leaves beside the kernel's counters
-  static std::atomic<int> oversize_words[64];
-  int oversize_capacity = dev < 64 ? oversize_words[dev].load(std::memory_order_acquire) : 0;
-  if (dev < 64 && oversize_capacity == 0) {
-    int optin = 0;
-    TBE_CUDA_TRY(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-    cudaFuncAttributes attr;
-    TBE_CUDA_TRY(cudaFuncGetAttributes(&attr, oversize_sort_kernel));
-    int dyn = optin - static_cast<int>(attr.sharedSizeBytes) - 256;
-    if (dyn < 0) dyn = 0;
-    TBE_CUDA_TRY(cudaFuncSetAttribute(oversize_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
-    oversize_capacity = dyn / 8 > 0 ? dyn / 8 : -1;  // -1: looked up, nothing fits
-    oversize_words[dev].store(oversize_capacity, std::memory_order_release);
+  // The queued-bucket sort keeps its word buffers and counters in opted-in dynamic shared memory.  Its
+  // grid is as many clusters as the device keeps resident at once, each walks the queue.  A skewed
+  // batch queues about one bucket per table and a bucket's sort is a chain of latencies more than of
+  // work, so the clusters are eight CTAs while those fit side by side and four beyond.
+  const int csize = T <= 32 ? kSortCluster : kSortCluster / 2;
+  static std::atomic<int> oversize_clusters[64][2];
+  int clusters = dev < 64 ? oversize_clusters[dev][csize == kSortCluster].load(std::memory_order_acquire) : 0;
+  cudaLaunchAttribute sort_attr;
+  sort_attr.id = cudaLaunchAttributeClusterDimension;
+  sort_attr.val.clusterDim.x = static_cast<unsigned>(csize);
+  sort_attr.val.clusterDim.y = 1;
+  sort_attr.val.clusterDim.z = 1;
+  cudaLaunchConfig_t sort_cfg = {};
+  sort_cfg.blockDim = dim3(kOversizeThreads);
+  sort_cfg.dynamicSmemBytes = kSortSmem;
+  sort_cfg.stream = stream;
+  sort_cfg.attrs = &sort_attr;
+  sort_cfg.numAttrs = 1;
+  if (clusters == 0) {
+    TBE_CUDA_TRY(cudaFuncSetAttribute(oversize_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(kSortSmem)));
+    sort_cfg.gridDim = dim3(static_cast<unsigned>(csize * device_sm_count()));
+    if (cudaOccupancyMaxActiveClusters(&clusters, oversize_sort_kernel, &sort_cfg) != cudaSuccess || clusters < 1) {
+      cudaGetLastError();
+      clusters = device_sm_count() / csize;  // one CTA per SM
+    }
+    if (clusters < 1) clusters = 1;
+    if (dev < 64) oversize_clusters[dev][csize == kSortCluster].store(clusters, std::memory_order_release);
   }
-  if (oversize_capacity < 0) oversize_capacity = 0;
-  const size_t oversize_smem = static_cast<size_t>(oversize_capacity) * 8;
   const bool wide = g.nb > kFewBuckets;
   constexpr size_t kScatterSmem = kScatterTile * sizeof(uint2) + 3 * kFewBuckets * sizeof(int32_t);
   constexpr size_t kScatterSmemWide = kScatterTileWide * sizeof(uint2) + 3 * kMaxBuckets * sizeof(int32_t);
@@ -851,14 +896,15 @@ int bucket_sort_plan(const int32_t* indices, const int32_t* offsets, int64_t T, 
   }
   TBE_CHECK_LAUNCH("bucket_rank_kernel");
   {
-    int blocks = device_sm_count();
-    if (blocks > qcap) blocks = qcap;
+    if (clusters > qcap) clusters = qcap;
+    if (clusters < 1) clusters = 1;
     int bag_bits = 0;
     while ((1ll << bag_bits) < B) ++bag_bits;
     KernelTimer timer("oversize_sort_kernel", stream);
-    oversize_sort_kernel<<<static_cast<unsigned>(blocks), kOversizeThreads, oversize_smem, stream>>>(
-        pairs, ws.keys, ws.vals, g.shift, bag_bits, layout.idx_bits, static_cast<int32_t>(B), queue_count,
-        ws.oversize, qcap, oversize_capacity);
+    sort_cfg.gridDim = dim3(static_cast<unsigned>(clusters * csize));
+    TBE_CUDA_TRY(cudaLaunchKernelEx(&sort_cfg, oversize_sort_kernel, pairs, ws.keys, ws.vals, g.shift, bag_bits,
+                                    layout.idx_bits, static_cast<int32_t>(B), static_cast<const int32_t*>(queue_count),
+                                    static_cast<const int2*>(ws.oversize), qcap));
   }
   TBE_CHECK_LAUNCH("oversize_sort_kernel");
   return TBE_OK;

@@ -70,7 +70,9 @@ def _table_sort_case(rng, T, E, B, Lmax, hot):
     (1, 1, 1, 1, False),
     (3, 17, 5, 6, False),              # a bucket is one row: nothing to sort inside it
     (2, 1000, 4096, 16, False),        # several slices and tiles per table
-    (2, 1000, 4096, 16, True),         # oversize buckets
+    (2, 1000, 4096, 16, True),         # oversize buckets (~24,000 pairs: sorted in a cluster's shared memory)
+    (1, 5000, 8192, 40, True),         # a bucket of ~120,000 pairs: beyond the cluster, passes through global memory
+    (40, 3000, 1024, 30, True),        # more queued buckets than resident clusters
     (5, 70000, 2048, 40, False),       # many buckets per table, rows not a power of two
     (5, 70000, 2048, 40, True),
     (70, 300000, 64, 30, False),       # more tables than one slice each can fill
@@ -136,6 +138,27 @@ def test_sgd_same_bits_with_either_sort(cuda_device):
         finally:
             _lib.call("tbe_set_tuning", b"bwd_sort", 0)
     assert torch.equal(out[0], out[1])
+
+
+@pytest.mark.parametrize("dtype,pooling", [(torch.float16, "sum"), (torch.float32, "mean")])
+def test_same_bits_with_tickets_or_a_fixed_stride(cuda_device, dtype, pooling):
+    """The apply kernel's warps take their tiles of the sorted entries either with a fixed stride or
+    from a ticket counter (the default once the pooled gradient outgrows L2); which warp processes a
+    tile must not show in the result.  ~300,000 lookups: more tiles than resident warps."""
+    c = to_device(make_case(T=8, E=20000, D=128, B=2048, Lmax=36, dtype=dtype, seed=21), cuda_device)
+    state = torch.rand(8 * 20000, device=cuda_device)
+    out = []
+    for mode in (1, 2):
+        _lib.call("tbe_set_tuning", b"bwd_stride", mode)
+        try:
+            out.append((_sgd(c, 0.05, pooling), *_adagrad(c, state, 0.05, 0.1, pooling)))
+        finally:
+            _lib.call("tbe_set_tuning", b"bwd_stride", 0)
+    for a, b in zip(*out):
+        assert torch.equal(a, b)
+    ref = oracle.sgd_step(c["weights"], c["table_offsets"], c["indices"], c["offsets"], c["grad"], 0.05, pooling,
+                          compute_dtype=torch.float32)
+    assert_close(out[1][0], ref, dtype)
 
 
 @pytest.mark.parametrize("D", [4, 8, 12, 64, 100, 128, 256, 260, 2048])
