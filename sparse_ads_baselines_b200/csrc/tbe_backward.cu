@@ -413,8 +413,9 @@ __device__ __forceinline__ Tile load_tile(const uint32_t* __restrict__ keys, con
 // pooling uses 1/L.
 //
 // Register budget: 64 (4 CTAs of 256 threads per SM).  Variants squeezed to 56 and 48 registers (9 and
-// 10 CTAs of 128 threads per SM) were measured 6 % to 30 % slower on the headline batch: the kernel
-// is not short of resident warps.
+// 10 CTAs of 128 threads per SM) were measured 6 % to 30 % slower on the headline batch, and two runs
+// in flight per lane group at 80 registers (3 CTAs per SM) 29 % slower: the kernel is short neither
+// of resident warps nor of loads in flight per warp.
 template <typename T, int VB, int OPT, bool MEAN, bool SR, int SEGS, int VPL>
 __global__ void __launch_bounds__(kBwdThreads, 4) run_kernel(const BwdArgs a) {
   using acc_t = typename Acc<T>::type;

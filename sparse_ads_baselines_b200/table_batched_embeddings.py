@@ -337,17 +337,6 @@ def _host_list(t):
     return v
 
 
-_zero_offsets = {}
-
-
-def _one_table_offsets(device):
-    z = _zero_offsets.get(device.index)
-    if z is None:
-        z = torch.zeros(1, dtype=torch.int32, device=device)
-        _zero_offsets[device.index] = z
-    return z
-
-
 def _mixed_tables(weights, table_offsets, dim_offsets, indices, offsets):
     """Yields (t, weights_t [E_t, D_t], indices_t, offsets_t, lo, hi, col0, D_t) per table."""
     _check_cuda("weights", weights)
@@ -409,25 +398,54 @@ def forward_mixed_D(weights, table_offsets, dim_offsets, total_D, indices, offse
     return out
 
 
+def _mixed_groups(tables, table_offsets_tensor, elem):
+    """Runs of consecutive tables of one width: ``(t0, t1, table_offsets_g)`` with the group's row
+    offsets (int32, on the device, relative to the group's first row).  Tables of one width that
+    follow each other share their layout with the uniform kernels -- rows of D elements back to
+    back, gradient columns side by side -- so a run takes ONE sort and ONE update launch."""
+    cache = getattr(table_offsets_tensor, "_tbe_mixed_groups", None)
+    key = tuple(tb[7] for tb in tables)
+    if cache is not None and cache[0] == key:
+        return cache[1]
+    groups, t0 = [], 0
+    dev = table_offsets_tensor.device
+    for t in range(1, len(tables) + 1):
+        if t == len(tables) or tables[t][7] != tables[t0][7]:
+            D = tables[t0][7]
+            rows = [(elem[u] - elem[t0]) // D for u in range(t0, t)]
+            groups.append((t0, t, torch.tensor(rows, dtype=torch.int32, device=dev)))
+            t0 = t
+    try:
+        table_offsets_tensor._tbe_mixed_groups = (key, groups)
+    except AttributeError:
+        pass
+    return groups
+
+
 def _backward_mixed(exact, grad_output, weights, table_offsets, table_dim_offsets, dim_offsets, total_D, indices,
                     offsets, indice_weights, optimizer_state, learning_rate, eps, stochastic_rounding):
     tables, B, T = _mixed_tables(weights, table_offsets, dim_offsets, indices, offsets)
     rows = _host_list(table_dim_offsets)
+    elem = _host_list(table_offsets)
     _require(tuple(grad_output.shape) == (B, int(total_D)), "grad_output must be [B, total_D]")
     if grad_output.stride(1) != 1:
         grad_output = grad_output.contiguous()
     grad_psw = None
     if indice_weights is not None:
         grad_psw = torch.empty(indices.shape, dtype=grad_output.dtype, device=weights.device)
-    to1 = _one_table_offsets(weights.device)
-    for (t, w_t, idx_t, off_t, lo, hi, col0, D) in tables:
-        g_t = grad_output[:, col0:col0 + D].unsqueeze(1)  # [B, 1, D_t], sample stride total_D
-        s_t = optimizer_state[rows[t]:rows[t + 1]]
+    for (t0, t1, to_g) in _mixed_groups(tables, table_offsets, elem):
+        D, col0, lo, hi = tables[t0][7], tables[t0][6], tables[t0][4], tables[t1 - 1][5]
+        Tg = t1 - t0
+        w_g = weights[elem[t0]:elem[t1]].view(-1, D)
+        idx_g = indices[lo:hi]
+        off_g = tables[t0][3] if Tg == 1 else offsets[t0 * B:t1 * B + 1] - lo
+        g_g = grad_output[:, col0:col0 + Tg * D].unflatten(1, (Tg, D))  # [B, Tg, D], sample stride total_D
+        s_g = optimizer_state[rows[t0]:rows[t1]]
         if exact:
-            backward_exact_adagrad(g_t, w_t, to1, idx_t, off_t, None, s_t, learning_rate, eps, stochastic_rounding, 1)
+            backward_exact_adagrad(g_g, w_g, to_g, idx_g, off_g, None, s_g, learning_rate, eps, stochastic_rounding, 1)
         else:
             psw = indice_weights[lo:hi] if indice_weights is not None else None
-            gp = backward_approx_adagrad(g_t, w_t, to1, idx_t, off_t, psw, s_t, learning_rate, eps, 200,
+            gp = backward_approx_adagrad(g_g, w_g, to_g, idx_g, off_g, psw, s_g, learning_rate, eps, 200,
                                          stochastic_rounding, 1)
             if gp is not None:
                 grad_psw[lo:hi] = gp

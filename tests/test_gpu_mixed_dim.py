@@ -9,9 +9,9 @@ from sparse_ads_baselines_b200 import table_batched_embeddings_ops as ops
 pytestmark = pytest.mark.gpu
 
 
-def _setup(T, B, L, fp16, seed, optimizer, replace):
+def _setup(T, B, L, fp16, seed, optimizer, replace, dims=None):
     rs = np.random.RandomState(seed)
-    dims = [int(rs.randint(1, 40)) * 4 for _ in range(T)]
+    dims = dims or [int(rs.randint(1, 40)) * 4 for _ in range(T)]
     rows = [int(rs.randint(60, 300)) for _ in range(T)]
     torch.manual_seed(seed)
     bs = [torch.nn.EmbeddingBag(E, D, mode="sum", sparse=True) for E, D in zip(rows, dims)]
@@ -48,12 +48,15 @@ def test_forward_mixed(cuda_device, T, B, L, fp16, weighted):
 
 @pytest.mark.parametrize("exact", [False, True])
 @pytest.mark.parametrize("fp16", [False, True])
-def test_backward_adagrad_mixed(cuda_device, exact, fp16):
-    T, B, L = 4, 6, 4
+@pytest.mark.parametrize("dims", [None, [32, 32, 32, 64, 16, 16, 128]])
+def test_backward_adagrad_mixed(cuda_device, exact, fp16, dims):
+    """``dims`` with runs of equal widths: consecutive tables of one width take one sort and one update
+    launch together (different row counts per table inside the run)."""
+    T, B, L = (len(dims), 9, 5) if dims else (4, 6, 4)
     opt = ops.Optimizer.EXACT_ROWWISE_ADAGRAD if exact else ops.Optimizer.APPROX_ROWWISE_ADAGRAD
     # exact: rows repeat; approximate: unique rows per table (the reference's racy kernel is only
     # defined there)
-    dims, rows, bs, xs, cc, indices, offsets = _setup(T, B, L, fp16, 11, opt, replace=exact)
+    dims, rows, bs, xs, cc, indices, offsets = _setup(T, B, L, fp16, 11, opt, replace=exact, dims=dims)
     fs = [b(x) for b, x in zip(bs, xs)]
     gos = [torch.randn_like(f) for f in fs]
     [f.backward(go) for f, go in zip(fs, gos)]
