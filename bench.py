@@ -405,6 +405,45 @@ def measure(args, w, rank, world, local_rank, rotate=ROTATE, with_e2e=True, with
         if backward:
             out.backward(grad)
 
+    # --graph: the step is captured once per rotating batch (extension functions on the batch's own
+    # buffers) and replayed; what is timed is then one graph launch per step
+    graphs, graph_info = [], {}
+
+    def raw_step(b, out_buf):
+        weights, to = module.embedding_weights.data, module.table_offsets
+        tbe.forward(weights, to, b["idx"], b["off"], None, 200, 2, False, pooling_mode=w.pooling, out=out_buf)
+        if not backward:
+            return
+        if w.optimizer == "sgd":
+            tbe.backward_sgd(grad, weights, to, b["idx"], b["off"], w.lr, 200, 2, False, pooling_mode=w.pooling)
+        else:
+            tbe.backward_exact_adagrad(grad, weights, to, b["idx"], b["off"], None, module.optimizer_state, w.lr,
+                                       w.eps, False, 1, pooling_mode=w.pooling)
+
+    def capture_graphs():
+        out_buf = torch.empty(w.B, w.T, w.D, dtype=tdt, device=device)
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            for b in batches:  # workspace and cached host copies exist before the capture starts
+                raw_step(b, out_buf)
+        torch.cuda.current_stream(device).wait_stream(side)
+        torch.cuda.synchronize()
+        for b in batches:
+            n0 = _lib.lib().tbe_kernel_launch_count()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                raw_step(b, out_buf)
+            graphs.append(g)
+            graph_info["kernels_per_step"] = _lib.lib().tbe_kernel_launch_count() - n0  # kernel nodes of one graph
+
+    if args.graph:
+        assert world == 1, "--graph is a one-GPU option"
+        _step_eager = step
+
+        def step(i):  # noqa: F811
+            graphs[i % rotate].replay()
+
     def timed(n_steps):
         """(device ms, host ms) of n_steps: CUDA events around the region, max over ranks; the host
         figure is the time the launching thread needed to enqueue the region."""
@@ -426,6 +465,8 @@ def measure(args, w, rank, world, local_rank, rotate=ROTATE, with_e2e=True, with
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms[0].item()), float(ms[1].item())
 
+    if args.graph:
+        capture_graphs()
     with ClockSampler(local_rank) as clocks:
         for i in range(args.warmup):
             step(i)
@@ -453,7 +494,11 @@ def measure(args, w, rank, world, local_rank, rotate=ROTATE, with_e2e=True, with
     sharded.check_exchange()
     value = N * world / (ms_per_step * 1e-3)
 
-    # one more identical region with per-launch events for the per-kernel breakdown
+    # one more identical region with per-launch events for the per-kernel breakdown (eager launches:
+    # the events are recorded by the library around each launch)
+    if args.graph:
+        launches = graph_info["kernels_per_step"] * args.steps  # replayed kernel nodes in one timed region
+        step = _step_eager
     _lib.kernel_timing_enable(True)
     timed(args.steps)
     kt = _lib.kernel_timing_read()
@@ -516,6 +561,9 @@ def measure(args, w, rank, world, local_rank, rotate=ROTATE, with_e2e=True, with
             "gpu_launches": int(launches),
             "library_launches_note": "gpu_launches counts this library's own kernels in one timed region; CUB sort/select launches are extra",
         }
+        if args.graph:
+            line["launch"] = ("one CUDA graph replay per step (%d kernel nodes); the per-kernel breakdown comes from "
+                              "an eager region" % graph_info["kernels_per_step"])
         if e2e is not None:
             line["e2e"] = e2e
         if cpu is not None:
@@ -804,6 +852,8 @@ def main():
                     help="multi-GPU runs of the target also time config 5 at its own shapes; this skips it")
     ap.add_argument("--plan-ahead", type=int, default=0,
                     help="1: sort the lookups for the backward on a side stream while the forward runs")
+    ap.add_argument("--graph", action="store_true",
+                    help="one GPU: capture the step in a CUDA graph per rotating batch and time the replays")
     ap.add_argument("--tune", default="", help="comma-separated knob=value pairs passed to tbe_set_tuning")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch of the dominant kernel from an ncu capture (profiles/), if known")
