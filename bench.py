@@ -761,7 +761,8 @@ def run_cached(args):
     E = int(w.E * args.cache_scale)
     cache_rows = int(2_000_000 * args.cache_scale) // 4 * 4
     m = LXUCachedEmbeddingBags(w.T, E, w.D, cache_rows=cache_rows, ways=4, policy="lru", learning_rate=w.lr,
-                               fp16=(w.dtype == "fp16"), pooling_mode=w.pooling)
+                               fp16=(w.dtype == "fp16"), pooling_mode=w.pooling, staged_fill=args.cache_fill == "staged",
+                               deferred_writeback=args.cache_fill == "deferred")
     gen = torch.Generator(device=device).manual_seed(1)
     data = m.embedding_weights.data
     for t in range(w.T):  # the device writes the host table through its mapping
@@ -774,8 +775,13 @@ def run_cached(args):
     grad = torch.randn(w.B, w.T, w.D, device=device, generator=gen).to(data.dtype)
     N = sum(b[2] for b in batches) / ROTATE
 
-    def step(i):
-        idx, off, _ = batches[i % ROTATE]
+    turn = [0]
+
+    def step(_):
+        # the batches keep rotating across the warm-up, the timed region and the regions after it, so
+        # that the cache statistics below do not depend on where a region happened to end
+        idx, off, _ = batches[turn[0] % ROTATE]
+        turn[0] += 1
         m(idx, off).backward(grad)
 
     for i in range(max(args.warmup, 2 * ROTATE)):  # warm the cache as well as the clocks
@@ -821,7 +827,8 @@ def run_cached(args):
         "cache": {"hit_rate": sum(h["hit_lookups"] for h in hit) / max(sum(h["lookups"] for h in hit), 1),
                   "row_hit_rate": sum(h["hit_rows"] for h in hit) / max(sum(h["rows"] for h in hit), 1),
                   "rows_fetched_per_step": sum(h["fetched"] for h in hit) / len(hit),
-                  "rows_uncached_per_step": sum(h["uncached"] for h in hit) / len(hit)},
+                  "rows_uncached_per_step": sum(h["uncached"] for h in hit) / len(hit),
+                  "fill": args.cache_fill},
         "clocks": clocks.summary(),
         "roofline": {"bound": "hbm", "kernel": top, "achieved": alg["step"] / (ms * 1e-3) / 1e9, "peak": peak,
                      "unit": "GB/s", "frac": alg["step"] / (ms * 1e-3) / 1e9 / peak, "peak_kind": peak_kind,
@@ -837,6 +844,9 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--cache-scale", type=float, default=1.0,
                     help="cfg4 only: scale rows per table and cache rows (1.0 = 10M rows x 32 tables, 81.9 GB pinned)")
+    ap.add_argument("--cache-fill", default="staged", choices=["staged", "direct", "deferred"],
+                    help="cfg4 only: how missed rows and victims cross the host link (staged copies through the copy "
+                         "engines; SM-issued loads and stores; the latter with write-backs on a side stream)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)

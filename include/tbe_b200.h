@@ -383,6 +383,26 @@ TBE_API int tbe_cache_prefetch(void* cache_rows, int32_t* tags, int32_t* last_us
  * `stats` is the array the prefetch wrote (its second word is the number of staged slots). */
 TBE_API int tbe_cache_writeback(const void* writeback_rows, const int32_t* writeback_ids, const int32_t* stats,
                                 void* host_rows, int64_t D, int dtype, void* stream);
+/* The same step with the rows travelling through the copy engines instead of SM-issued loads and
+ * stores (a kernel reading random rows of an 80 GB mapped table gets ~13 GB/s out of the host link,
+ * copies of contiguous pinned buffers 55 GB/s).  Per round of up to stage_rows claims: the dirty
+ * victims are packed into stage_device and copied out, worker threads of the library gather the new
+ * rows from the table (host_rows_on_host: the table's address on the HOST) into stage_host, one copy
+ * brings them in and a kernel inserts them, and the workers scatter the victims into the table.
+ *   stage_device  device buffer of tbe_cache_stage_bytes(stage_rows, D, dtype, 0) bytes
+ *   stage_host    pinned host buffer of tbe_cache_stage_bytes(stage_rows, D, dtype, 1) bytes
+ * Unlike every other entry point this one WAITS for the stream (it has to learn the number of
+ * claims) and returns with the host table up to date for the evicted rows; host_rows stays the
+ * device-mapped address, which the lookup and the update still use for rows left uncached.  Results
+ * are those of tbe_cache_prefetch bit for bit. */
+TBE_API int64_t tbe_cache_stage_bytes(int64_t stage_rows, int64_t D, int dtype, int on_host);
+TBE_API int tbe_cache_prefetch_staged(void* cache_rows, int32_t* tags, int32_t* last_use, int32_t* use_count,
+                                      uint8_t* dirty, void* host_rows, const int32_t* table_offsets,
+                                      const int32_t* indices, const int32_t* offsets, int32_t* locations,
+                                      int32_t* stats, int64_t T, int64_t B, int64_t D, int64_t N,
+                                      int64_t total_rows, int64_t num_sets, int ways, int dtype, int policy,
+                                      int now, void* host_rows_on_host, void* stage_device, void* stage_host,
+                                      int64_t stage_rows, void* workspace, int64_t workspace_bytes, void* stream);
 /* Pooled forward reading every row through `locations` (sum / mean, fp16 / fp32). */
 TBE_API int tbe_cache_forward(const void* cache_rows, const void* host_rows,
                               const int32_t* table_offsets, const int32_t* indices,

@@ -60,6 +60,9 @@ SIGNATURES = {
     "tbe_cache_prefetch": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64,
                                   _i64, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _i64, _vp]),
     "tbe_cache_writeback": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _vp]),
+    "tbe_cache_stage_bytes": (_i64, [_i64, _i64, _i32, _i32]),
+    "tbe_cache_prefetch_staged": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64,
+                                         _i64, _i64, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _i64, _vp, _i64, _vp]),
     "tbe_cache_forward": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
     "tbe_cache_backward_sgd": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32,
                                       _i32, _f32, _vp, _i64, _vp]),

@@ -8,6 +8,8 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <sys/mman.h>
+#include <utility>
 
 #include "tbe_common.cuh"
 
@@ -98,7 +100,7 @@ int64_t device_l2_bytes() {
 }
 }  // namespace tbe
 
-extern "C" int tbe_abi_version(void) { return 4; }
+extern "C" int tbe_abi_version(void) { return 5; }
 
 extern "C" const char* tbe_last_error_string(void) { return tbe::g_error; }
 
@@ -182,14 +184,46 @@ extern "C" int tbe_free_managed(void* ptr) {
   return TBE_OK;
 }
 
+namespace tbe {
+namespace {
+// Large host-mapped allocations made from anonymous memory: {aligned address -> (mapping base, mapping length)}.
+std::mutex g_mapped_mu;
+std::map<void*, std::pair<void*, size_t>> g_mapped;
+constexpr size_t kHugePage = 2u << 20;
+}  // namespace
+}  // namespace tbe
+
 extern "C" int tbe_alloc_host_mapped(void** host_ptr, void** device_ptr, int64_t bytes) {
   TBE_REQUIRE(host_ptr && device_ptr && bytes > 0, "tbe_alloc_host_mapped: bad arguments");
   void* h = nullptr;
-  TBE_CUDA_TRY(cudaHostAlloc(&h, static_cast<size_t>(bytes), cudaHostAllocMapped | cudaHostAllocPortable));
+  // A table of a gigabyte or more comes from anonymous memory that asks for transparent huge pages and
+  // is then registered with CUDA.  The GPU does not care, but the host side of the staged cache fill
+  // gathers and scatters random rows of it, and with 4 KB pages every such row is a TLB miss whose
+  // page walk misses the caches as well.  (Best effort: where that is refused, cudaHostAlloc below.)
+  if (bytes >= (1ll << 30)) {
+    const size_t len = (static_cast<size_t>(bytes) + 2 * tbe::kHugePage - 1) & ~(tbe::kHugePage - 1);
+    void* base = mmap(nullptr, len, PROT_READ | PROT_WRITE, MAP_PRIVATE | MAP_ANONYMOUS, -1, 0);
+    if (base != MAP_FAILED) {
+      void* aligned = reinterpret_cast<void*>((reinterpret_cast<uintptr_t>(base) + tbe::kHugePage - 1) &
+                                              ~static_cast<uintptr_t>(tbe::kHugePage - 1));
+      madvise(aligned, len - tbe::kHugePage, MADV_HUGEPAGE);
+      if (cudaHostRegister(aligned, static_cast<size_t>(bytes), cudaHostRegisterMapped | cudaHostRegisterPortable) ==
+          cudaSuccess) {
+        std::lock_guard<std::mutex> lk(tbe::g_mapped_mu);
+        tbe::g_mapped[aligned] = std::make_pair(base, len);
+        h = aligned;
+      } else {
+        cudaGetLastError();
+        munmap(base, len);
+      }
+    }
+  }
+  if (h == nullptr)
+    TBE_CUDA_TRY(cudaHostAlloc(&h, static_cast<size_t>(bytes), cudaHostAllocMapped | cudaHostAllocPortable));
   void* d = nullptr;
   cudaError_t e = cudaHostGetDevicePointer(&d, h, 0);
   if (e != cudaSuccess) {
-    cudaFreeHost(h);
+    tbe_free_host_mapped(h);
     return tbe::fail(TBE_ERR_CUDA, "cudaHostGetDevicePointer failed: %s", cudaGetErrorString(e));
   }
   *host_ptr = h;
@@ -198,6 +232,22 @@ extern "C" int tbe_alloc_host_mapped(void** host_ptr, void** device_ptr, int64_t
 }
 
 extern "C" int tbe_free_host_mapped(void* host_ptr) {
+  tbe::host_pool_wait();  // no worker may still be writing evicted rows into the table
+  std::pair<void*, size_t> mapping(nullptr, 0);
+  {
+    std::lock_guard<std::mutex> lk(tbe::g_mapped_mu);
+    auto it = tbe::g_mapped.find(host_ptr);
+    if (it != tbe::g_mapped.end()) {
+      mapping = it->second;
+      tbe::g_mapped.erase(it);
+    }
+  }
+  if (mapping.first != nullptr) {
+    cudaError_t e = cudaHostUnregister(host_ptr);
+    munmap(mapping.first, mapping.second);
+    if (e != cudaSuccess) return tbe::fail(TBE_ERR_CUDA, "cudaHostUnregister failed: %s", cudaGetErrorString(e));
+    return TBE_OK;
+  }
   TBE_CUDA_TRY(cudaFreeHost(host_ptr));
   return TBE_OK;
 }

@@ -64,6 +64,9 @@ enum Tuning {
 
 int device_sm_count();
 int64_t device_l2_bytes();
+// Waits for host-side work the library still has in flight (the staged cache fill scatters evicted
+// rows into the host table in the background).
+void host_pool_wait();
 
 // Optional per-launch timing: when enabled (tbe_kernel_timing_enable), every launch site brackets
 // its kernel with two CUDA events on the launch stream; tbe_kernel_timing_read sums them per name.

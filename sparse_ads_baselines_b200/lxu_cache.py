@@ -57,7 +57,8 @@ class LXUCachedEmbeddingBags(nn.Module):
     ``ways``-way set-associative HBM cache of ``cache_rows`` rows; fused exact SGD."""
 
     def __init__(self, num_tables, num_embeddings, embedding_dim, cache_rows, ways=4, policy="lru",
-                 learning_rate=0.01, fp16=False, pooling_mode="sum", deferred_writeback=False):
+                 learning_rate=0.01, fp16=False, pooling_mode="sum", deferred_writeback=False, staged_fill=True,
+                 stage_rows=131072):
         super().__init__()
         assert policy in _POLICY and pooling_mode in ("sum", "mean")
         assert ways in (1, 2, 4, 8, 16, 32) and cache_rows % ways == 0
@@ -69,8 +70,9 @@ class LXUCachedEmbeddingBags(nn.Module):
         self.learning_rate, self.pooling_mode = learning_rate, pooling_mode
         proto = torch.empty(1, device=device, dtype=dtype)
         # pinned host memory mapped into the device: the GPU reads and writes it directly
-        self.embedding_weights = nn.Parameter(
-            tbe_ext.new_host_mapped_tensor(proto, (total_rows, embedding_dim)), requires_grad=False)
+        table = tbe_ext.new_host_mapped_tensor(proto, (total_rows, embedding_dim))
+        self._table_host_ptr = table._tbe_host_ptr  # the same memory as the CPU addresses it
+        self.embedding_weights = nn.Parameter(table, requires_grad=False)
         self.register_buffer("table_offsets", torch.arange(num_tables, dtype=torch.int32, device=device) * num_embeddings)
         self.register_buffer("cache_rows", torch.zeros(cache_rows, embedding_dim, dtype=dtype, device=device),
                              persistent=False)
@@ -87,7 +89,15 @@ class LXUCachedEmbeddingBags(nn.Module):
         # the host table on a side stream while the lookup runs; the next prefetch (and flush) wait for
         # them.  Off by default: SM-issued traffic to mapped host memory shares one ~25 GB/s link budget,
         # so the deferred stores only move the time from the fill kernel into the lookup they overlap.
-        self.deferred_writeback = deferred_writeback
+        self.deferred_writeback = deferred_writeback and not staged_fill
+        # staged fill (default): missed rows and dirty victims cross the host link as contiguous copies
+        # through the copy engines, gathered / scattered in the host table by the library's worker
+        # threads, instead of as SM-issued loads and stores of single rows; the prefetch then waits for
+        # the stream once per step
+        self.staged_fill = staged_fill
+        self.stage_rows = int(stage_rows)
+        self._stage_dev = None
+        self._stage_host = None
         self._wb_rows = None
         self._wb_ids = None
         self._wb_stream = None
@@ -120,6 +130,26 @@ class LXUCachedEmbeddingBags(nn.Module):
             if self._wb_stream is None:
                 self._wb_stream = torch.cuda.Stream(dev, priority=-1)
         defer = self.deferred_writeback and stage > 0
+        if self.staged_fill and N > 0:
+            if self._stage_dev is None:
+                dt = tbe_ext._DTYPES[w.dtype]
+                nd = _lib.lib().tbe_cache_stage_bytes(self.stage_rows, self.embedding_dim, dt, 0)
+                nh = _lib.lib().tbe_cache_stage_bytes(self.stage_rows, self.embedding_dim, dt, 1)
+                if nd < 0 or nh < 0:
+                    raise _lib.TBEError("tbe_cache_stage_bytes", min(nd, nh), _lib.last_error())
+                self._stage_dev = torch.empty(nd, dtype=torch.uint8, device=dev)
+                self._stage_host = torch.empty(nh, dtype=torch.uint8).pin_memory()
+            with torch.cuda.device(dev):
+                _lib.call("tbe_cache_prefetch_staged", self.cache_rows.data_ptr(), self.tags.data_ptr(),
+                          self.last_use.data_ptr(), self.use_count.data_ptr(), self.dirty.data_ptr(), w.data_ptr(),
+                          self.table_offsets.data_ptr(), indices.data_ptr(), offsets.data_ptr(),
+                          self._locations.data_ptr(), self._stats.data_ptr(), self.num_tables, self.batch_of(offsets),
+                          self.embedding_dim, N, w.size(0), self.num_sets, self.ways, tbe_ext._DTYPES[w.dtype],
+                          _POLICY[self.policy], self.step, self._table_host_ptr, self._stage_dev.data_ptr(),
+                          self._stage_host.data_ptr(), self.stage_rows, self._workspace.data_ptr(),
+                          self._workspace.numel(), tbe_ext._stream(dev))
+            self._last_n = N
+            return
         with torch.cuda.device(dev):
             main = torch.cuda.current_stream(dev)
             self._wait_writeback(dev)  # this step's fetches must see the previous step's write-backs

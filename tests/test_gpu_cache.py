@@ -54,10 +54,12 @@ def test_slot_bookkeeping_matches_cpu_model(cuda_device, policy, ways):
 
 @pytest.mark.parametrize("fp16", [False, True])
 @pytest.mark.parametrize("pooling", ["sum", "mean"])
-@pytest.mark.parametrize("deferred", [False, True])
-def test_cached_module_is_transparent(cuda_device, fp16, pooling, deferred):
+@pytest.mark.parametrize("fill", ["direct", "deferred", "staged", "staged_rounds"])
+def test_cached_module_is_transparent(cuda_device, fp16, pooling, fill):
     """Several fwd + SGD steps through a small cache (evictions, write-backs, uncached rows) give the
-    outputs and the final table of the uncached device-resident module and of the oracle."""
+    outputs and the final table of the uncached device-resident module and of the oracle, whichever way
+    the rows cross the host link: SM-issued loads and stores (direct, deferred write-backs) or staged
+    copies with the host gathering and scattering rows (one round, or several rounds of 3 claims)."""
     T, E, D, B, Lmax, lr = 3, 60, 32, 8, 6, 0.05
     dtype = torch.float16 if fp16 else torch.float32
     torch.manual_seed(0)
@@ -65,7 +67,8 @@ def test_cached_module_is_transparent(cuda_device, fp16, pooling, deferred):
                                           pooling_mode=pooling).cuda()
     plain.embedding_weights.data.uniform_(-1, 1)
     cached = LXUCachedEmbeddingBags(T, E, D, cache_rows=16, ways=4, policy="lru", learning_rate=lr, fp16=fp16,
-                                    pooling_mode=pooling, deferred_writeback=deferred)
+                                    pooling_mode=pooling, deferred_writeback=fill == "deferred",
+                                    staged_fill=fill.startswith("staged"), stage_rows=3 if fill == "staged_rounds" else 4096)
     cached.embedding_weights.data.copy_(plain.embedding_weights.data)
     w_ref = plain.embedding_weights.detach().cpu().clone()
     to = [t * E for t in range(T)]
