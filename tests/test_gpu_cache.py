@@ -94,6 +94,32 @@ def test_cached_module_is_transparent(cuda_device, fp16, pooling, fill):
                                **tol)
 
 
+@pytest.mark.parametrize("stage_rows", [131072, 5000])
+def test_large_rounds_of_the_staged_fill(cuda_device, stage_rows):
+    """Tens of thousands of misses per step: one large round of the staged fill (its gather handed to
+    the copy engine in pieces), or several rounds with 5000 staging rows.  Three steps of lookups + SGD through a cache that keeps evicting must leave the
+    table the plain device-resident module computes, bit for bit (fp32, same kernels' arithmetic)."""
+    T, E, D, B, L, lr = 2, 100_000, 32, 2048, 8, 0.05
+    torch.manual_seed(2)
+    plain = ops.TableBatchedEmbeddingBags(T, E, D, optimizer=ops.Optimizer.SGD, learning_rate=lr).cuda()
+    plain.embedding_weights.data.uniform_(-1, 1)
+    cached = LXUCachedEmbeddingBags(T, E, D, cache_rows=32768, ways=4, policy="lru", learning_rate=lr,
+                                    staged_fill=True, stage_rows=stage_rows)
+    cached.embedding_weights.data.copy_(plain.embedding_weights.data)
+    rng = np.random.default_rng(7)
+    off = torch.from_numpy((np.arange(T * B + 1) * L).astype(np.int32)).cuda()
+    for step in range(3):
+        idx = torch.from_numpy(rng.integers(0, E, size=T * B * L).astype(np.int32)).cuda()
+        go = torch.randn(B, T, D, device="cuda")
+        out_p, out_c = plain(idx, off), cached(idx, off)
+        torch.testing.assert_close(out_c, out_p.detach(), rtol=1e-5, atol=1e-5)
+        assert cached.last_stats()["fetched"] > 8192
+        out_p.backward(go)
+        out_c.backward(go)
+    sd = cached.state_dict()
+    torch.testing.assert_close(sd["embedding_weights"].cpu(), plain.embedding_weights.detach().cpu(), rtol=1e-5, atol=1e-5)
+
+
 def test_empty_batch_clears_every_counter(cuda_device):
     """A step without lookups after a step with uncached rows reports zeros in all five counters."""
     T, E, D, B = 2, 40, 8, 4
