@@ -756,9 +756,14 @@ namespace {
 class HostPool {
  public:
   static HostPool& get() {
-    static HostPool* pool = new HostPool();
+    static HostPool* pool = [] {
+      HostPool* p = new HostPool();
+      existing_.store(p, std::memory_order_release);
+      return p;
+    }();
     return *pool;
   }
+  static HostPool* existing() { return existing_.load(std::memory_order_acquire); }  // null until first used
   // fn(begin, end) over [0, n) in chunks, on the workers and the calling thread; returns when all of it is done
   void parallel_for(int64_t n, const std::function<void(int64_t, int64_t)>& fn) {
     if (n <= 0) return;
@@ -852,6 +857,7 @@ class HostPool {
       job->done.fetch_add(e - b, std::memory_order_release);
     }
   }
+  static std::atomic<HostPool*> existing_;
   std::mutex call_mu_, mu_;
   std::condition_variable cv_work_;
   std::shared_ptr<Job> job_, background_;
@@ -859,6 +865,8 @@ class HostPool {
   std::atomic<uint64_t> generation_{0};
   unsigned workers_ = 0;
 };
+
+std::atomic<HostPool*> HostPool::existing_{nullptr};
 
 // A whole row written into the host table.  The row is overwritten completely and not read again by
 // this thread, so on x86-64 it goes out with streaming stores: no read-for-ownership of lines that
@@ -920,7 +928,9 @@ int stage_streams(StageStreams** res) {
 
 }  // namespace
 
-void host_pool_wait() { HostPool::get().wait(); }
+void host_pool_wait() {
+  if (HostPool* pool = HostPool::existing()) pool->wait();  // (never creates the threads)
+}
 
 namespace {
 
@@ -953,6 +963,9 @@ int cache_prefetch_impl(const char* who, void* cache_rows, int32_t* tags, int32_
     return fail(TBE_ERR_WORKSPACE_TOO_SMALL, "%s: workspace has %lld bytes, %lld needed", who,
                 (long long)workspace_bytes, (long long)cs.total);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  // victims of an earlier staged prefetch that are still on their way into the host table must be
+  // there before this step fetches from it (by either path)
+  host_pool_wait();
   TBE_CUDA_TRY(cudaMemsetAsync(cs.ws.counters, 0, 64, stream));
   if (N == 0) {
     TBE_CUDA_TRY(cudaMemsetAsync(stats, 0, 5 * sizeof(int32_t), stream));
@@ -1061,7 +1074,6 @@ int cache_prefetch_impl(const char* who, void* cache_rows, int32_t* tags, int32_
     TBE_CUDA_TRY(cudaStreamSynchronize(stream));
     const int64_t nclaims = h_counters[2];
     HostPool& pool = HostPool::get();
-    pool.wait();  // the last step's victims are in the table before any row is gathered from it
     char* table = staged->host_table;
     for (int64_t c0 = 0; c0 < nclaims; c0 += R) {
       const int64_t n = nclaims - c0 < R ? nclaims - c0 : R;
