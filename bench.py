@@ -346,17 +346,21 @@ def host_link_rates(device, world):
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0.record()
-        for _ in range(8):
-            dst.copy_(src, non_blocking=True)
-        t1.record()
-        torch.cuda.synchronize()
-        ms = torch.tensor([t0.elapsed_time(t1)], device=device)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        out[name + "_gbs_per_rank"] = 8 * nbytes / (float(ms.item()) * 1e-3) / 1e9
-    out["note"] = "256 MiB pinned copies, all %d ranks at once, slowest rank" % world
+        best = 0.0
+        for _ in range(3):  # the best of three rounds of eight copies: a ceiling, not an average
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(8):
+                dst.copy_(src, non_blocking=True)
+            t1.record()
+            torch.cuda.synchronize()
+            ms = torch.tensor([t0.elapsed_time(t1)], device=device)
+            if world > 1:
+                dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            best = max(best, 8 * nbytes / (float(ms.item()) * 1e-3) / 1e9)
+        out[name + "_gbs_per_rank"] = best
+    out["note"] = ("256 MiB pinned copies, one direction at a time, all %d ranks at once, slowest rank, best of three "
+                   "rounds of eight copies" % world)
     return out
 
 
@@ -535,9 +539,10 @@ def measure(args, w, rank, world, local_rank, rotate=ROTATE, with_e2e=True, with
         else:
             e2e = run_e2e_sharded(args, w, sharded, batches, grad, backward, device, world)
         e2e["host_link"] = host_link_rates(device, world)
-        per_rank_bytes = max(e2e["h2d_bytes_per_step"], e2e["d2h_bytes_per_step"]) / world
-        link = min(e2e["host_link"]["h2d_gbs_per_rank"], e2e["host_link"]["d2h_gbs_per_rank"])
-        e2e["host_link"]["ceiling_lookups_per_s"] = N * world / (per_rank_bytes / (link * 1e9))
+        # a step cannot be shorter than its bytes in either direction at that direction's rate
+        floor_s = max(e2e["h2d_bytes_per_step"] / world / (e2e["host_link"]["h2d_gbs_per_rank"] * 1e9),
+                      e2e["d2h_bytes_per_step"] / world / (e2e["host_link"]["d2h_gbs_per_rank"] * 1e9))
+        e2e["host_link"]["ceiling_lookups_per_s"] = N * world / floor_s
 
     cpu = None
     if with_cpu and rank == 0 and world == 1 and not args.no_cpu_baseline:
