@@ -825,14 +825,15 @@ class HostPool {
   }
   HostPool() {
     const unsigned hc = std::thread::hardware_concurrency();
-    workers_ = hc > 1 ? (hc - 1 < 15 ? hc - 1 : 15) : 0;
+    // (two cores stay free for the caller's launching thread and its autograd thread)
+    workers_ = hc > 3 ? (hc - 2 < 15 ? hc - 2 : 15) : (hc > 1 ? 1 : 0);
     for (unsigned i = 0; i < workers_; ++i) std::thread([this] { loop(); }).detach();
   }
   void loop() {
     uint64_t seen = 0;
     for (;;) {
       for (int spin = 0; generation_.load(std::memory_order_acquire) == seen; ++spin) {
-        if (spin < 20000) {
+        if (spin < 4000) {  // ~0.2 ms: the pieces of a gather follow each other closely, the scatter soon after
           relax();
         } else {
           std::unique_lock<std::mutex> lk(mu_);
