@@ -359,9 +359,38 @@ def host_link_rates(device, world):
                 dist.all_reduce(ms, op=dist.ReduceOp.MAX)
             best = max(best, 32 * nbytes / (float(ms.item()) * 1e-3) / 1e9)
         out[name + "_gbs_per_rank"] = best
+    # both directions at once, as in the real step (two streams, 32 copies each way)
+    h2 = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    d2 = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    s_a, s_b = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    best_in = best_out = 0.0
+    for _ in range(3):
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        with torch.cuda.stream(s_a):
+            ev[0].record()
+            for _ in range(32):
+                d.copy_(h, non_blocking=True)
+            ev[1].record()
+        with torch.cuda.stream(s_b):
+            ev[2].record()
+            for _ in range(32):
+                h2.copy_(d2, non_blocking=True)
+            ev[3].record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([ev[0].elapsed_time(ev[1]), ev[2].elapsed_time(ev[3])], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        best_in = max(best_in, 32 * nbytes / (float(ms[0].item()) * 1e-3) / 1e9)
+        best_out = max(best_out, 32 * nbytes / (float(ms[1].item()) * 1e-3) / 1e9)
+    out["h2d_gbs_per_rank_both_ways"] = best_in
+    out["d2h_gbs_per_rank_both_ways"] = best_out
     out["note"] = ("32 MiB pinned copies, one direction at a time, all %d ranks at once, slowest rank, best of three "
-                   "rounds of 32 copies; run-to-run spread of these rates on one box is about 10 %%, so the ceiling "
-                   "derived from them is a guide, not a bound to the last percent" % world)
+                   "rounds of 32 copies, then both directions at once on two streams (the *_both_ways rates); "
+                   "run-to-run spread of these rates on one box is about 10 %%.  The real step lies between the two "
+                   "ceilings derived from them: its copies in the two directions overlap part of the time" % world)
     return out
 
 
@@ -544,6 +573,9 @@ def measure(args, w, rank, world, local_rank, rotate=ROTATE, with_e2e=True, with
         floor_s = max(e2e["h2d_bytes_per_step"] / world / (e2e["host_link"]["h2d_gbs_per_rank"] * 1e9),
                       e2e["d2h_bytes_per_step"] / world / (e2e["host_link"]["d2h_gbs_per_rank"] * 1e9))
         e2e["host_link"]["ceiling_lookups_per_s"] = N * world / floor_s
+        floor_both = max(e2e["h2d_bytes_per_step"] / world / (e2e["host_link"]["h2d_gbs_per_rank_both_ways"] * 1e9),
+                         e2e["d2h_bytes_per_step"] / world / (e2e["host_link"]["d2h_gbs_per_rank_both_ways"] * 1e9))
+        e2e["host_link"]["ceiling_both_ways_lookups_per_s"] = N * world / floor_both
 
     cpu = None
     if with_cpu and rank == 0 and world == 1 and not args.no_cpu_baseline:
